@@ -140,13 +140,18 @@ class CacheManager:
         self.seqs: Dict[Hashable, SeqCache] = {}
         self.dtype = dtype
         self.device = device
-        # Storage: per group [planes, 2 (k, v), pages, page_size, kv_heads, head_dim]; per state plane [max_seqs, *shape].
-        self.kv: List[Optional[torch.Tensor]] = [None] * ngroups
+        # Storage: per group keys [planes, pages, page_size, kv_heads, head_dim] and values [..., kv_heads, v_head_dim]
+        # (none for a group that keeps no values); per state plane [max_seqs, *shape].
+        self.keys: List[Optional[torch.Tensor]] = [None] * ngroups
+        self.values: List[Optional[torch.Tensor]] = [None] * ngroups
         self.state: List[Optional[torch.Tensor]] = [None] * len(layout.state_planes)
         if device is not None:
             for g, (spec, planes) in enumerate(zip(layout.groups, layout.planes_per_group)):
-                self.kv[g] = torch.zeros((planes, 2, num_pages[g], page_size, spec.kv_heads, spec.head_dim),
-                                         dtype=dtype, device=device)
+                self.keys[g] = torch.zeros((planes, num_pages[g], page_size, spec.kv_heads, spec.head_dim),
+                                           dtype=dtype, device=device)
+                if spec.value_dim > 0:
+                    self.values[g] = torch.zeros((planes, num_pages[g], page_size, spec.kv_heads, spec.value_dim),
+                                                 dtype=dtype, device=device)
             for i, s in enumerate(layout.state_planes):
                 self.state[i] = torch.zeros((max_seqs, *s.shape), dtype=getattr(torch, s.dtype), device=device)
 
@@ -276,12 +281,13 @@ class CacheManager:
         return hit[1]
 
     def plane_kv(self, group: int, plane: int):
-        """(k, v) storage of one plane, each ``[pages * page_size, kv_heads, head_dim]``."""
-        t = self.kv[group]
-        if t is None:
+        """(k, v) storage of one plane: ``[pages * page_size, kv_heads, head_dim]`` and ``[..., kv_heads, v_head_dim]``
+        (``v`` is ``None`` for a group that keeps no values)."""
+        if self.keys[group] is None:
             raise CacheError("the cache has no device storage")
-        k, v = t[plane, 0], t[plane, 1]
-        return k.view(-1, k.shape[-2], k.shape[-1]), v.view(-1, v.shape[-2], v.shape[-1])
+        k = self.keys[group][plane]
+        v = self.values[group][plane] if self.values[group] is not None else None
+        return k.view(-1, k.shape[-2], k.shape[-1]), (None if v is None else v.view(-1, v.shape[-2], v.shape[-1]))
 
     # ---- accounting --------------------------------------------------------------------------
     def free_pages(self, group: int = 0) -> int:

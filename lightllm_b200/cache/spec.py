@@ -13,12 +13,19 @@ from typing import Dict, List, Optional, Sequence, Tuple
 
 @dataclass(frozen=True)
 class KVSpec:
-    """Keys and values per token: ``kv_heads * head_dim`` each.  ``window`` = how many of the
-    latest positions (the token itself included) stay visible; ``None`` = all of them."""
+    """Keys and values per token: ``kv_heads * head_dim`` keys and ``kv_heads * v_head_dim`` values.
+    ``window`` = how many of the latest positions (the token itself included) stay visible; ``None`` = all of
+    them.  ``v_head_dim``: ``None`` = as wide as the keys; 0 = no values are kept (a mixer that reads its values
+    out of the key rows, e.g. attention over a shared latent)."""
 
     kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    v_head_dim: Optional[int] = None
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_head_dim is None else self.v_head_dim
 
 
 @dataclass(frozen=True)
@@ -66,7 +73,8 @@ class CacheLayout:
                 owner = layout.refs[src]
                 want = spec.kv if spec else None
                 have = layout.groups[owner.group] if owner.group is not None else None
-                if want is not None and (have is None or (want.kv_heads, want.head_dim) != (have.kv_heads, have.head_dim)):
+                if want is not None and (have is None or (want.kv_heads, want.head_dim, want.value_dim)
+                                         != (have.kv_heads, have.head_dim, have.value_dim)):
                     raise ValueError(
                         f"run entry {i} reads the cache of entry {src}, whose geometry {have} does not fit {want}")
                 if want is not None and have.window is not None and (want.window is None or want.window > have.window):
@@ -91,8 +99,14 @@ class CacheLayout:
 
     def bytes_per_page(self, group: int, page_size: int, element_bytes: int) -> int:
         s = self.groups[group]
-        return 2 * self.planes_per_group[group] * page_size * s.kv_heads * s.head_dim * element_bytes
+        return self.planes_per_group[group] * page_size * s.kv_heads * (s.head_dim + s.value_dim) * element_bytes
 
     def bytes_per_token(self, element_bytes: int) -> int:
-        return sum(2 * n * s.kv_heads * s.head_dim * element_bytes
+        return sum(n * s.kv_heads * (s.head_dim + s.value_dim) * element_bytes
                    for s, n in zip(self.groups, self.planes_per_group))
+
+    def state_bytes_per_request(self) -> int:
+        """Bytes of fixed-size state that one live request holds, over all state planes."""
+        import math
+        width = {"float32": 4, "bfloat16": 2, "float16": 2, "int32": 4}
+        return sum(math.prod(s.shape) * width.get(s.dtype, 4) for s in self.state_planes)

@@ -98,10 +98,15 @@ class ModelConfig:
 
 
 def architecture_name(raw: Dict[str, Any], where: str = "config.json") -> str:
-    """``architectures[0]`` of a config dictionary (src/model/model_config.cpp:69-84)."""
+    """``architectures[0]`` of a config dictionary (src/model/model_config.cpp:69-84), or the string under
+    ``architecture`` in files that name their one architecture so."""
+    single = raw.get("architecture")
+    if "architectures" not in raw and isinstance(single, str) and single:
+        return single
     archs = raw.get("architectures")
     if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
-        raise ConfigError(f"{where}: required key 'architectures' must be a non-empty list of names")
+        raise ConfigError(f"{where}: required key 'architectures' must be a non-empty list of names "
+                          "(or 'architecture' a name)")
     return archs[0]
 
 

@@ -38,8 +38,10 @@ struct AttnParams {
     const int* span_pos;
     const int* block_table;
     int max_pages, page_size, Hq, Hkv, hd, window, BQ, nsplit;
+    int hdv;              // width of a value row and of an output row (hd for ordinary attention)
+    const float* sinks;   // [Hq] or null: exp(sinks[h]) joins the softmax denominator once, with no key and no value
     float scale;
-    float* part_acc;  // [tiles, Hkv, nsplit, BQ*G, hd]
+    float* part_acc;  // [tiles, Hkv, nsplit, BQ*G, hdv]
     float* part_ml;   // [tiles, Hkv, nsplit, BQ*G, 2]
 };
 
@@ -48,16 +50,16 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_kernel(AttnParams
     extern __shared__ float smem[];
     const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
     const int G = p.Hq / p.Hkv;
-    const int hd = p.hd;
+    const int hd = p.hd, hdv = p.hdv;
     const int nqv = p.BQ * G;
     const int kstride = hd | 1;
     float* Qs = smem;                       // [nqv][hd]
-    float* Acc = Qs + (size_t)nqv * hd;     // [nqv][hd]
-    float* Ms = Acc + (size_t)nqv * hd;     // [nqv]
+    float* Acc = Qs + (size_t)nqv * hd;     // [nqv][hdv]
+    float* Ms = Acc + (size_t)nqv * hdv;    // [nqv]
     float* Ls = Ms + nqv;                   // [nqv]
     float* Ks = Ls + nqv;                   // [BK][kstride]
-    float* Vs = Ks + BK * kstride;          // [BK][hd]
-    float* Ps = Vs + BK * hd;               // [NWARPS][BK]
+    float* Vs = Ks + BK * kstride;          // [BK][hdv]
+    float* Ps = Vs + BK * hdv;              // [NWARPS][BK]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int span = p.tile_span[tile];
@@ -89,8 +91,8 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_kernel(AttnParams
         float val = 0.0f;
         if (r < nrows) val = llb_to_float(q[((size_t)(row0 + r) * p.Hq + kvh * G + g) * hd + d]);
         Qs[i] = val;
-        Acc[i] = 0.0f;
     }
+    for (int i = threadIdx.x; i < nqv * hdv; i += blockDim.x) Acc[i] = 0.0f;
     for (int i = threadIdx.x; i < nqv; i += blockDim.x) {
         Ms[i] = -INFINITY;
         Ls[i] = 0.0f;
@@ -105,16 +107,12 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_kernel(AttnParams
                 const int page = bt[kpos / p.page_size];
                 const size_t slot = (size_t)page * p.page_size + (kpos % p.page_size);
                 const T* kr = kc + (slot * p.Hkv + kvh) * hd;
-                const T* vr = vc + (slot * p.Hkv + kvh) * hd;
-                for (int d = lane; d < hd; d += 32) {
-                    Ks[j * kstride + d] = llb_to_float(kr[d]);
-                    Vs[j * hd + d] = llb_to_float(vr[d]);
-                }
+                const T* vr = vc + (slot * p.Hkv + kvh) * hdv;
+                for (int d = lane; d < hd; d += 32) Ks[j * kstride + d] = llb_to_float(kr[d]);
+                for (int d = lane; d < hdv; d += 32) Vs[j * hdv + d] = llb_to_float(vr[d]);
             } else {
-                for (int d = lane; d < hd; d += 32) {
-                    Ks[j * kstride + d] = 0.0f;
-                    Vs[j * hd + d] = 0.0f;
-                }
+                for (int d = lane; d < hd; d += 32) Ks[j * kstride + d] = 0.0f;
+                for (int d = lane; d < hdv; d += 32) Vs[j * hdv + d] = 0.0f;
             }
         }
         __syncthreads();
@@ -141,11 +139,11 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_kernel(AttnParams
             const float l_new = Ls[v] * corr + llb_warp_sum(pr);
             Ps[warp * BK + lane] = pr;
             __syncwarp();
-            for (int d = lane; d < hd; d += 32) {
-                float a = Acc[(size_t)v * hd + d] * corr;
+            for (int d = lane; d < hdv; d += 32) {
+                float a = Acc[(size_t)v * hdv + d] * corr;
 #pragma unroll 8
-                for (int j = 0; j < BK; ++j) a = fmaf(Ps[warp * BK + j], Vs[j * hd + d], a);
-                Acc[(size_t)v * hd + d] = a;
+                for (int j = 0; j < BK; ++j) a = fmaf(Ps[warp * BK + j], Vs[j * hdv + d], a);
+                Acc[(size_t)v * hdv + d] = a;
             }
             __syncwarp();
             if (lane == 0) {
@@ -162,15 +160,17 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_kernel(AttnParams
         for (int v = warp; v < nqv; v += NWARPS) {
             const int r = v / G, g = v - r * G;
             if (r >= nrows) continue;
-            const float inv = 1.0f / Ls[v];
-            T* o = out + ((size_t)(row0 + r) * p.Hq + kvh * G + g) * hd;
-            for (int d = lane; d < hd; d += 32) o[d] = llb_from_float<T>(Acc[(size_t)v * hd + d] * inv);
+            float den = Ls[v];
+            if (p.sinks) den += expf(p.sinks[kvh * G + g] - Ms[v]);
+            const float inv = 1.0f / den;
+            T* o = out + ((size_t)(row0 + r) * p.Hq + kvh * G + g) * hdv;
+            for (int d = lane; d < hdv; d += 32) o[d] = llb_from_float<T>(Acc[(size_t)v * hdv + d] * inv);
         }
     } else {
         const size_t base = (((size_t)tile * p.Hkv + kvh) * p.nsplit + split) * nqv;
         for (int v = warp; v < nqv; v += NWARPS) {
-            float* pa = p.part_acc + (base + v) * hd;
-            for (int d = lane; d < hd; d += 32) pa[d] = Acc[(size_t)v * hd + d];
+            float* pa = p.part_acc + (base + v) * hdv;
+            for (int d = lane; d < hdv; d += 32) pa[d] = Acc[(size_t)v * hdv + d];
             if (lane == 0) {
                 p.part_ml[(base + v) * 2 + 0] = Ms[v];
                 p.part_ml[(base + v) * 2 + 1] = Ls[v];
@@ -210,13 +210,14 @@ __global__ void __launch_bounds__(32) attention_merge_kernel(AttnParams p) {
             L += w * p.part_ml[idx * 2 + 1];
         }
         L = llb_warp_sum(L);
+        if (p.sinks) L += expf(p.sinks[head] - M);
         __syncwarp();
         const float inv = 1.0f / L;
-        for (int d = lane; d < p.hd; d += 32) {
+        for (int d = lane; d < p.hdv; d += 32) {
             float a = 0.0f;
 #pragma unroll 8
-            for (int s = 0; s < p.nsplit; ++s) a = fmaf(wsm[s], p.part_acc[((base0 + s) * nqv + v) * p.hd + d], a);
-            out[((size_t)(row0 + r) * p.Hq + head) * p.hd + d] = llb_from_float<T>(a * inv);
+            for (int s = 0; s < p.nsplit; ++s) a = fmaf(wsm[s], p.part_acc[((base0 + s) * nqv + v) * p.hdv + d], a);
+            out[((size_t)(row0 + r) * p.Hq + head) * p.hdv + d] = llb_from_float<T>(a * inv);
         }
         __syncwarp();
     }
@@ -263,11 +264,11 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_decode_kernel(AttnParams p)
     constexpr int VEC = Vec16<T>::N;
     const int tile = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
     const int G = p.Hq / p.Hkv;
-    const int hd = p.hd;
+    const int hd = p.hd, hdv = p.hdv;
     float* Qs = smem;                                   // [G][hd]
     float* Ps = Qs + G * hd;                            // [NWARPS][GMAX][32]
-    float* Wacc = Ps + NWARPS * GMAX * 32;              // [NWARPS][G][hd]
-    float* Wml = Wacc + NWARPS * G * hd;                // [NWARPS][G][2]
+    float* Wacc = Ps + NWARPS * GMAX * 32;              // [NWARPS][G][hdv]
+    float* Wml = Wacc + NWARPS * G * hdv;               // [NWARPS][G][2]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int span = p.tile_span[tile];
@@ -301,7 +302,8 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_decode_kernel(AttnParams p)
         for (int n = 0; n < NPMAX; ++n) acc[g][n][0] = acc[g][n][1] = 0.0f;
     }
     float* myP = Ps + warp * GMAX * 32;
-    const size_t row_stride = (size_t)p.Hkv * hd;
+    const size_t row_stride = (size_t)p.Hkv * hd;        // of a key row
+    const size_t vrow_stride = (size_t)p.Hkv * hdv;      // of a value row
 
     for (int kb = klo + warp * BK; kb < khi; kb += NWARPS * BK) {
         const int kpos = kb + lane;
@@ -318,7 +320,7 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_decode_kernel(AttnParams p)
             for (int j = 0; j < BK; ++j) {
                 const size_t sj = __shfl_sync(0xffffffffu, slot, j);
                 v0r[j] = v1r[j] = 0.0f;
-                if (j < nkeys && d < hd) Vec16<T>::load2(vc + sj * row_stride + (size_t)kvh * hd + d, v0r[j], v1r[j]);
+                if (j < nkeys && d < hdv) Vec16<T>::load2(vc + sj * vrow_stride + (size_t)kvh * hdv + d, v0r[j], v1r[j]);
             }
         }
         float dot[GMAX];
@@ -374,11 +376,11 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_decode_kernel(AttnParams p)
 #pragma unroll 8
             for (int j = 0; j < nkeys; ++j) {
                 const size_t sj = __shfl_sync(0xffffffffu, slot, j);
-                const T* vr = vc + sj * row_stride + (size_t)kvh * hd;
+                const T* vr = vc + sj * vrow_stride + (size_t)kvh * hdv;
 #pragma unroll
                 for (int n = 0; n < NPMAX; ++n) {
                     const int d = n * 64 + 2 * lane;
-                    if (d < hd) {
+                    if (d < hdv) {
                         float v0, v1;
                         Vec16<T>::load2(vr + d, v0, v1);
 #pragma unroll
@@ -403,9 +405,9 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_decode_kernel(AttnParams p)
 #pragma unroll
             for (int n = 0; n < NPMAX; ++n) {
                 const int d = n * 64 + 2 * lane;
-                if (d < hd) {
-                    Wacc[(warp * G + g) * hd + d] = acc[g][n][0];
-                    Wacc[(warp * G + g) * hd + d + 1] = acc[g][n][1];
+                if (d < hdv) {
+                    Wacc[(warp * G + g) * hdv + d] = acc[g][n][0];
+                    Wacc[(warp * G + g) * hdv + d + 1] = acc[g][n][1];
                 }
             }
             if (lane == 0) {
@@ -416,8 +418,8 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_decode_kernel(AttnParams p)
     }
     __syncthreads();
     const size_t base = (((size_t)tile * p.Hkv + kvh) * p.nsplit + split) * G;
-    for (int i = threadIdx.x; i < G * hd; i += blockDim.x) {
-        const int g = i / hd, d = i - g * hd;
+    for (int i = threadIdx.x; i < G * hdv; i += blockDim.x) {
+        const int g = i / hdv, d = i - g * hdv;
         float M = -INFINITY;
 #pragma unroll
         for (int w = 0; w < NWARPS; ++w) M = fmaxf(M, Wml[(w * G + g) * 2]);
@@ -428,13 +430,14 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_decode_kernel(AttnParams p)
             if (mw != -INFINITY) {
                 const float e = expf(mw - M);
                 L += e * Wml[(w * G + g) * 2 + 1];
-                a += e * Wacc[(w * G + g) * hd + d];
+                a += e * Wacc[(w * G + g) * hdv + d];
             }
         }
         if (p.nsplit == 1) {
-            ((T*)p.out)[((size_t)row0 * p.Hq + kvh * G + g) * hd + d] = llb_from_float<T>(a / L);
+            if (p.sinks) L += expf(p.sinks[kvh * G + g] - M);
+            ((T*)p.out)[((size_t)row0 * p.Hq + kvh * G + g) * hdv + d] = llb_from_float<T>(a / L);
         } else {
-            p.part_acc[(base + g) * hd + d] = a;
+            p.part_acc[(base + g) * hdv + d] = a;
             if (d == 0) {
                 p.part_ml[(base + g) * 2] = M;
                 p.part_ml[(base + g) * 2 + 1] = L;
@@ -443,14 +446,14 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_decode_kernel(AttnParams p)
     }
 }
 
-size_t decode_smem_bytes(int G, int gmax, int hd) {
-    return ((size_t)G * hd + (size_t)NWARPS * gmax * 32 + (size_t)NWARPS * G * hd + (size_t)NWARPS * G * 2) * sizeof(float);
+size_t decode_smem_bytes(int G, int gmax, int hd, int hdv) {
+    return ((size_t)G * hd + (size_t)NWARPS * gmax * 32 + (size_t)NWARPS * G * hdv + (size_t)NWARPS * G * 2) * sizeof(float);
 }
 
 template <typename T, int GMAX>
 int launch_decode_np(const AttnParams& p, dim3 grid, size_t smem, cudaStream_t stream) {
-    if (p.hd <= 64) paged_decode_kernel<T, GMAX, 1><<<grid, NWARPS * 32, smem, stream>>>(p);
-    else if (p.hd <= 128) paged_decode_kernel<T, GMAX, 2><<<grid, NWARPS * 32, smem, stream>>>(p);
+    if (p.hdv <= 64) paged_decode_kernel<T, GMAX, 1><<<grid, NWARPS * 32, smem, stream>>>(p);
+    else if (p.hdv <= 128) paged_decode_kernel<T, GMAX, 2><<<grid, NWARPS * 32, smem, stream>>>(p);
     else paged_decode_kernel<T, GMAX, 4><<<grid, NWARPS * 32, smem, stream>>>(p);
     return llb_check_launch("paged_decode");
 }
@@ -460,31 +463,31 @@ template <typename T>
 bool decode_eligible(const AttnParams& p) {
     const int G = p.Hq / p.Hkv;
     const int gmax = G <= 1 ? 1 : G <= 2 ? 2 : G <= 4 ? 4 : G <= 8 ? 8 : 16;
-    return p.BQ == 1 && G <= 16 && p.hd <= 256 && p.hd % 2 == 0 && (p.hd * sizeof(T)) % 16 == 0 &&
+    return p.BQ == 1 && G <= 16 && p.hd <= 256 && p.hdv <= 256 && p.hdv % 2 == 0 && (p.hd * sizeof(T)) % 16 == 0 &&
            ((uintptr_t)p.k_cache % 16 == 0) && ((uintptr_t)p.v_cache % 16 == 0) &&
-           decode_smem_bytes(G, gmax, p.hd) <= 48 * 1024;
+           decode_smem_bytes(G, gmax, p.hd, p.hdv) <= 48 * 1024;
 }
 
 template <typename T>
 int launch_decode(const AttnParams& p, int num_tiles, cudaStream_t stream) {
     const int G = p.Hq / p.Hkv;
     dim3 grid(num_tiles, p.Hkv, p.nsplit);
-    if (G <= 1) return launch_decode_np<T, 1>(p, grid, decode_smem_bytes(G, 1, p.hd), stream);
-    if (G <= 2) return launch_decode_np<T, 2>(p, grid, decode_smem_bytes(G, 2, p.hd), stream);
-    if (G <= 4) return launch_decode_np<T, 4>(p, grid, decode_smem_bytes(G, 4, p.hd), stream);
-    if (G <= 8) return launch_decode_np<T, 8>(p, grid, decode_smem_bytes(G, 8, p.hd), stream);
-    return launch_decode_np<T, 16>(p, grid, decode_smem_bytes(G, 16, p.hd), stream);
+    if (G <= 1) return launch_decode_np<T, 1>(p, grid, decode_smem_bytes(G, 1, p.hd, p.hdv), stream);
+    if (G <= 2) return launch_decode_np<T, 2>(p, grid, decode_smem_bytes(G, 2, p.hd, p.hdv), stream);
+    if (G <= 4) return launch_decode_np<T, 4>(p, grid, decode_smem_bytes(G, 4, p.hd, p.hdv), stream);
+    if (G <= 8) return launch_decode_np<T, 8>(p, grid, decode_smem_bytes(G, 8, p.hd, p.hdv), stream);
+    return launch_decode_np<T, 16>(p, grid, decode_smem_bytes(G, 16, p.hd, p.hdv), stream);
 }
 
-size_t attention_smem_bytes(int BQ, int G, int hd) {
+size_t attention_smem_bytes(int BQ, int G, int hd, int hdv) {
     const size_t nqv = (size_t)BQ * G;
-    const size_t floats = 2 * nqv * hd + 2 * nqv + (size_t)BK * (hd | 1) + (size_t)BK * hd + NWARPS * BK;
+    const size_t floats = nqv * hd + nqv * hdv + 2 * nqv + (size_t)BK * (hd | 1) + (size_t)BK * hdv + NWARPS * BK;
     return floats * sizeof(float);
 }
 
 template <typename T>
 int launch_attention(const AttnParams& p, int num_tiles, cudaStream_t stream) {
-    const size_t smem = attention_smem_bytes(p.BQ, p.Hq / p.Hkv, p.hd);
+    const size_t smem = attention_smem_bytes(p.BQ, p.Hq / p.Hkv, p.hd, p.hdv);
     LLB_REQUIRE(smem <= 220 * 1024, "attention: BQ=%d with %d heads per group and head_dim %d needs %zu bytes of "
                 "shared memory; use a smaller BQ", p.BQ, p.Hq / p.Hkv, p.hd, smem);
     static size_t configured = 0;  // largest opt-in so far for this instantiation
@@ -516,7 +519,12 @@ int launch_attention(const AttnParams& p, int num_tiles, cudaStream_t stream) {
 
 // Shared memory one block needs for the given tile height; the caller picks BQ with it.
 LLB_EXPORT long long llb_attention_smem_bytes(int BQ, int group, int hd) {
-    return (long long)attention_smem_bytes(BQ, group, hd);
+    return (long long)attention_smem_bytes(BQ, group, hd, hd);
+}
+
+// The same with value rows of another width than the keys'.
+LLB_EXPORT long long llb_attention_smem_bytes_v(int BQ, int group, int hd, int hdv) {
+    return (long long)attention_smem_bytes(BQ, group, hd, hdv);
 }
 
 // Floats of scratch that nsplit > 1 needs: acc and (m, l).
@@ -524,17 +532,20 @@ LLB_EXPORT long long llb_attention_scratch_floats(int num_tiles, int Hq, int hd,
     return (long long)num_tiles * Hq * BQ * nsplit * (hd + 2);
 }
 
-// q, out [T, Hq, hd]; k_cache, v_cache [slots, Hkv, hd] with slot = page*page_size + offset;
+// q [T, Hq, hd]; out [T, Hq, hdv]; k_cache [slots, Hkv, hd], v_cache [slots, Hkv, hdv] with slot = page*page_size +
+// offset (v_cache may be k_cache itself with hdv == hd: values read out of the key rows);
 // tile_span, tile_q0 [num_tiles]; span_row, span_len, span_pos [S]; block_table [S, max_pages].
-// window <= 0 means every earlier key is visible.  scratch: llb_attention_scratch_floats floats
+// window <= 0 means every earlier key is visible.  sinks [Hq] float or null: exp(sinks[h]) is added once to head h's
+// softmax denominator (a logit without key or value, not scaled).  scratch: num_tiles*Hq*BQ*nsplit*(hdv+2) floats
 // when nsplit > 1, else unused.
-LLB_EXPORT int llb_paged_attention(const void* q, const void* k_cache, const void* v_cache, void* out, int dtype,
-                                   const int* tile_span, const int* tile_q0, int num_tiles, const int* span_row,
-                                   const int* span_len, const int* span_pos, const int* block_table,
-                                   int max_pages, int page_size, int Hq, int Hkv, int hd, int window, float scale,
-                                   int BQ, int nsplit, float* scratch, cudaStream_t stream) {
+LLB_EXPORT int llb_paged_attention_ex(const void* q, const void* k_cache, const void* v_cache, void* out, int dtype,
+                                      const int* tile_span, const int* tile_q0, int num_tiles, const int* span_row,
+                                      const int* span_len, const int* span_pos, const int* block_table,
+                                      int max_pages, int page_size, int Hq, int Hkv, int hd, int hdv,
+                                      const float* sinks, int window, float scale, int BQ, int nsplit, float* scratch,
+                                      cudaStream_t stream) {
     if (num_tiles == 0) return 0;
-    LLB_REQUIRE(num_tiles > 0 && Hq > 0 && Hkv > 0 && hd > 0 && page_size > 0 && max_pages > 0 && BQ > 0,
+    LLB_REQUIRE(num_tiles > 0 && Hq > 0 && Hkv > 0 && hd > 0 && hdv > 0 && page_size > 0 && max_pages > 0 && BQ > 0,
                 "attention: bad sizes");
     LLB_REQUIRE(Hq % Hkv == 0, "attention: %d query heads are not a multiple of %d kv heads", Hq, Hkv);
     LLB_REQUIRE(nsplit >= 1 && nsplit <= MERGE_MAX_SPLITS && Hkv <= 65535,
@@ -546,11 +557,23 @@ LLB_EXPORT int llb_paged_attention(const void* q, const void* k_cache, const voi
     p.span_row = span_row; p.span_len = span_len; p.span_pos = span_pos; p.block_table = block_table;
     p.max_pages = max_pages; p.page_size = page_size; p.Hq = Hq; p.Hkv = Hkv; p.hd = hd;
     p.window = window; p.BQ = BQ; p.nsplit = nsplit; p.scale = scale;
+    p.hdv = hdv; p.sinks = sinks;
     p.part_acc = scratch;
-    p.part_ml = scratch ? scratch + (size_t)num_tiles * Hq * BQ * nsplit * hd : nullptr;
+    p.part_ml = scratch ? scratch + (size_t)num_tiles * Hq * BQ * nsplit * hdv : nullptr;
     if (dtype == LLB_F32) return launch_attention<float>(p, num_tiles, stream);
     if (dtype == LLB_BF16) return launch_attention<__nv_bfloat16>(p, num_tiles, stream);
     return llb_fail("attention: unknown dtype %d", dtype);
+}
+
+// Ordinary attention: values as wide as keys, no sinks.
+LLB_EXPORT int llb_paged_attention(const void* q, const void* k_cache, const void* v_cache, void* out, int dtype,
+                                   const int* tile_span, const int* tile_q0, int num_tiles, const int* span_row,
+                                   const int* span_len, const int* span_pos, const int* block_table,
+                                   int max_pages, int page_size, int Hq, int Hkv, int hd, int window, float scale,
+                                   int BQ, int nsplit, float* scratch, cudaStream_t stream) {
+    return llb_paged_attention_ex(q, k_cache, v_cache, out, dtype, tile_span, tile_q0, num_tiles, span_row, span_len,
+                                  span_pos, block_table, max_pages, page_size, Hq, Hkv, hd, hd, nullptr, window, scale,
+                                  BQ, nsplit, scratch, stream);
 }
 
 // ---------------------------------------------------------------------------------------------

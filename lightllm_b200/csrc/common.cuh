@@ -53,4 +53,15 @@ __device__ __forceinline__ float llb_warp_max(float v) {
 // x / (1 + exp(-x)) in float, as src/ops/elementwise.cu:27-33 computes SiLU.
 __device__ __forceinline__ float llb_silu(float x) { return x / (1.0f + expf(-x)); }
 
+// The gated activations of a feed-forward, on a (gate, up) pair in float.
+//   kind 0  SiLU gate:            silu(g) * u
+//   kind 1  clamped swish gate:   g' = min(g, limit), u' = clamp(u, -limit, limit);  g' * sigmoid(alpha * g') * (u' + up_shift)
+enum LlbGlu { LLB_GLU_SILU = 0, LLB_GLU_CLAMPED_SWISH = 1 };
+__device__ __forceinline__ float llb_glu(float g, float u, int kind, float alpha, float limit, float up_shift) {
+    if (kind == LLB_GLU_SILU) return llb_silu(g) * u;
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.0f + expf(-alpha * g)) * (u + up_shift);
+}
+
 static inline int llb_ceil_div(int a, int b) { return (a + b - 1) / b; }

@@ -1,0 +1,88 @@
+// Gates: the activation of a gated feed-forward on interleaved (gate, up) columns, and the gate on a mixer's heads
+// (optionally after a unit-RMS norm of every head).  All arithmetic is float; inputs and outputs float or bf16.
+#include "common.cuh"
+
+namespace {
+
+template <typename T>
+__global__ void glu_act_kernel(const T* __restrict__ in, T* __restrict__ out, long long n, int kind, float alpha,
+                               float limit, float up_shift) {
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const float g = llb_to_float(in[2 * i]), u = llb_to_float(in[2 * i + 1]);
+        out[i] = llb_from_float<T>(llb_glu(g, u, kind, alpha, limit, up_shift));
+    }
+}
+
+// One warp per (token, head): y = x (or x / rms(x) over the head), times act(gate).
+template <typename TX, typename TG, typename TO>
+__global__ void __launch_bounds__(256) head_gate_kernel(const TX* __restrict__ x, const TG* __restrict__ gate,
+                                                        long long gate_stride, TO* __restrict__ out, int T, int H, int hd,
+                                                        int unit_rms, float eps, int per_head, int act) {
+    const int lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= (long long)T * H) return;
+    const int t = (int)(item / H), h = (int)(item - (long long)t * H);
+    const TX* xr = x + ((size_t)t * H + h) * hd;
+    TO* o = out + ((size_t)t * H + h) * hd;
+    float inv = 1.0f;
+    if (unit_rms) {
+        float ss = 0.0f;
+        for (int d = lane; d < hd; d += 32) {
+            const float v = llb_to_float(xr[d]);
+            ss += v * v;
+        }
+        inv = 1.0f / sqrtf(llb_warp_sum(ss) / (float)hd + eps);
+    }
+    const TG* gr = gate + (size_t)t * gate_stride + (per_head ? h : (size_t)h * hd);
+    for (int d = lane; d < hd; d += 32) {
+        const float z = llb_to_float(gr[per_head ? 0 : d]);
+        const float a = act == 0 ? 1.0f / (1.0f + expf(-z)) : llb_silu(z);
+        o[d] = llb_from_float<TO>(llb_to_float(xr[d]) * inv * a);
+    }
+}
+
+template <typename TX, typename TG, typename TO>
+int launch_head_gate(const void* x, const void* gate, long long gate_stride, void* out, int T, int H, int hd,
+                     int unit_rms, float eps, int per_head, int act, cudaStream_t s) {
+    const long long items = (long long)T * H;
+    head_gate_kernel<TX, TG, TO><<<(unsigned)((items + 7) / 8), 256, 0, s>>>(
+        (const TX*)x, (const TG*)gate, gate_stride, (TO*)out, T, H, hd, unit_rms, eps, per_head, act);
+    return llb_check_launch("head_gate");
+}
+
+}  // namespace
+
+// in [M, 2I] with (gate, up) in columns (2j, 2j+1); out [M, I] = glu(gate, up) (see llb_glu in common.cuh).
+LLB_EXPORT int llb_glu_act(const void* in, void* out, int dtype, int M, int I, int kind, float alpha, float limit,
+                           float up_shift, cudaStream_t stream) {
+    if (M == 0 || I == 0) return 0;
+    LLB_REQUIRE(M > 0 && I > 0 && in && out, "glu_act: bad arguments");
+    const long long n = (long long)M * I;
+    const int blocks = (int)((n + 255) / 256 < 2368 ? (n + 255) / 256 : 2368);
+    if (dtype == LLB_F32)
+        glu_act_kernel<float><<<blocks, 256, 0, stream>>>((const float*)in, (float*)out, n, kind, alpha, limit, up_shift);
+    else if (dtype == LLB_BF16)
+        glu_act_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)in, (__nv_bfloat16*)out, n, kind,
+                                                                   alpha, limit, up_shift);
+    else
+        return llb_fail("glu_act: unknown dtype %d", dtype);
+    return llb_check_launch("glu_act");
+}
+
+// x [T, H, hd] (float or the activation dtype); gate: row t starts at gate + t * gate_stride and holds H values
+// (per_head) or H*hd; out [T, H, hd] in the activation dtype.  out = (unit_rms ? x / sqrt(mean_head(x^2) + eps) : x)
+// * act(gate), act 0 = sigmoid, 1 = SiLU.  x_dtype: dtype of x; dtype: of gate and out.
+LLB_EXPORT int llb_head_gate(const void* x, int x_dtype, const void* gate, long long gate_stride, void* out, int dtype,
+                             int T, int H, int hd, int unit_rms, float eps, int per_head, int act, cudaStream_t stream) {
+    if (T == 0) return 0;
+    LLB_REQUIRE(T > 0 && H > 0 && hd > 0 && x && gate && out, "head_gate: bad arguments");
+    LLB_REQUIRE(act == 0 || act == 1, "head_gate: unknown activation %d", act);
+    if (x_dtype == LLB_F32 && dtype == LLB_F32)
+        return launch_head_gate<float, float, float>(x, gate, gate_stride, out, T, H, hd, unit_rms, eps, per_head, act, stream);
+    if (x_dtype == LLB_F32 && dtype == LLB_BF16)
+        return launch_head_gate<float, __nv_bfloat16, __nv_bfloat16>(x, gate, gate_stride, out, T, H, hd, unit_rms, eps, per_head, act, stream);
+    if (x_dtype == LLB_BF16 && dtype == LLB_BF16)
+        return launch_head_gate<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(x, gate, gate_stride, out, T, H, hd, unit_rms, eps, per_head, act, stream);
+    return llb_fail("head_gate: unsupported dtypes %d, %d", x_dtype, dtype);
+}

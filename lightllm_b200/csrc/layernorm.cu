@@ -1,0 +1,119 @@
+// Layer normalisation with weight and bias over rows of a float stream, optionally only over a list of rows, and
+// optionally added into a float destination (a norm on a branch's output: h += LN(branch) in one pass).
+//
+//     mean = sum_d x_d / D;  var = sum_d (x_d - mean)^2 / D;  y_d = (x_d - mean) / sqrt(var + eps) * w_d + b_d
+//
+// All statistics are float; the variance is taken from the deviations (second pass over the row, which stays in
+// registers when it fits), not from E[x^2] - mean^2.
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ float block_sum(float v, float* part, float* total) {
+    v = llb_warp_sum(v);
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = v;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        float t = threadIdx.x < (blockDim.x >> 5) ? part[threadIdx.x] : 0.0f;
+        t = llb_warp_sum(t);
+        if (threadIdx.x == 0) *total = t;
+    }
+    __syncthreads();
+    const float r = *total;
+    __syncthreads();
+    return r;
+}
+
+template <typename TW, typename TO, int PER_THREAD, bool ACCUMULATE>
+__global__ void __launch_bounds__(256) layernorm_kernel(const float* __restrict__ x, const TW* __restrict__ w,
+                                                        const TW* __restrict__ b, TO* __restrict__ out,
+                                                        const int* __restrict__ rows, int D, float eps) {
+    __shared__ float part[32];
+    __shared__ float total;
+    const int r = blockIdx.x;
+    const float* xr = x + (size_t)(rows ? rows[r] : r) * D;
+    TO* o = out + (size_t)r * D;
+    float v[PER_THREAD > 0 ? PER_THREAD : 1];
+    float s = 0.0f;
+    if (PER_THREAD > 0) {
+#pragma unroll
+        for (int i = 0; i < PER_THREAD; ++i) {
+            const int d = threadIdx.x + i * blockDim.x;
+            v[i] = d < D ? xr[d] : 0.0f;
+            s += v[i];
+        }
+    } else {
+        for (int d = threadIdx.x; d < D; d += blockDim.x) s += xr[d];
+    }
+    const float mean = block_sum(s, part, &total) / (float)D;
+    float q = 0.0f;
+    if (PER_THREAD > 0) {
+#pragma unroll
+        for (int i = 0; i < PER_THREAD; ++i) {
+            const int d = threadIdx.x + i * blockDim.x;
+            const float c = d < D ? v[i] - mean : 0.0f;
+            q += c * c;
+        }
+    } else {
+        for (int d = threadIdx.x; d < D; d += blockDim.x) {
+            const float c = xr[d] - mean;
+            q += c * c;
+        }
+    }
+    const float inv = 1.0f / sqrtf(block_sum(q, part, &total) / (float)D + eps);
+    if (PER_THREAD > 0) {
+#pragma unroll
+        for (int i = 0; i < PER_THREAD; ++i) {
+            const int d = threadIdx.x + i * blockDim.x;
+            if (d < D) {
+                float y = (v[i] - mean) * inv * llb_to_float(w[d]) + llb_to_float(b[d]);
+                if (ACCUMULATE) y += llb_to_float(o[d]);
+                o[d] = llb_from_float<TO>(y);
+            }
+        }
+    } else {
+        for (int d = threadIdx.x; d < D; d += blockDim.x) {
+            float y = (xr[d] - mean) * inv * llb_to_float(w[d]) + llb_to_float(b[d]);
+            if (ACCUMULATE) y += llb_to_float(o[d]);
+            o[d] = llb_from_float<TO>(y);
+        }
+    }
+}
+
+template <typename TW, typename TO, bool ACC>
+int launch_ln(const float* x, const void* w, const void* b, void* out, const int* rows, int R, int D, float eps,
+              cudaStream_t s) {
+    const int threads = 256;
+    if (D <= threads * 4)
+        layernorm_kernel<TW, TO, 4, ACC><<<R, threads, 0, s>>>(x, (const TW*)w, (const TW*)b, (TO*)out, rows, D, eps);
+    else if (D <= threads * 16)
+        layernorm_kernel<TW, TO, 16, ACC><<<R, threads, 0, s>>>(x, (const TW*)w, (const TW*)b, (TO*)out, rows, D, eps);
+    else
+        layernorm_kernel<TW, TO, 0, ACC><<<R, threads, 0, s>>>(x, (const TW*)w, (const TW*)b, (TO*)out, rows, D, eps);
+    return llb_check_launch("layernorm");
+}
+
+template <typename TW>
+int dispatch_ln(int out_dtype, int accumulate, const float* x, const void* w, const void* b, void* out, const int* rows,
+                int R, int D, float eps, cudaStream_t s) {
+    if (out_dtype == LLB_F32)
+        return accumulate ? launch_ln<TW, float, true>(x, w, b, out, rows, R, D, eps, s)
+                          : launch_ln<TW, float, false>(x, w, b, out, rows, R, D, eps, s);
+    if (out_dtype == LLB_BF16)
+        return accumulate ? launch_ln<TW, __nv_bfloat16, true>(x, w, b, out, rows, R, D, eps, s)
+                          : launch_ln<TW, __nv_bfloat16, false>(x, w, b, out, rows, R, D, eps, s);
+    return llb_fail("layernorm: unknown output dtype %d", out_dtype);
+}
+
+}  // namespace
+
+// x float [*, D]; w, b [D] (float or bf16, the same for both); out [R, D]; rows: R source rows of x or null for
+// rows 0..R-1; accumulate != 0: out += LN(x) (out must not be x).
+LLB_EXPORT int llb_layernorm(const float* x, const void* w, const void* b, int w_dtype, void* out, int out_dtype,
+                             const int* rows, int R, int D, float eps, int accumulate, cudaStream_t stream) {
+    if (R == 0) return 0;
+    LLB_REQUIRE(R > 0 && D > 0 && x && w && b && out, "layernorm: bad arguments R=%d D=%d", R, D);
+    if (w_dtype == LLB_F32) return dispatch_ln<float>(out_dtype, accumulate, x, w, b, out, rows, R, D, eps, stream);
+    if (w_dtype == LLB_BF16) return dispatch_ln<__nv_bfloat16>(out_dtype, accumulate, x, w, b, out, rows, R, D, eps, stream);
+    return llb_fail("layernorm: unknown weight dtype %d", w_dtype);
+}

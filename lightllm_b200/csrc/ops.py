@@ -17,7 +17,7 @@ from . import build as _build
 
 F32, BF16 = 0, 1
 EPI_STORE, EPI_STORE_F32, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2, 3
-ABI_VERSION = 21
+ABI_VERSION = 22
 
 _lib: Optional[ctypes.CDLL] = None
 
@@ -215,11 +215,12 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, slot_mapping: Opti
                                    T, num_heads, hkv, head_dim, 1 if write_kv else 0, _stream()))
 
 
-def attention_smem_bytes(bq: int, group: int, head_dim: int) -> int:
-    return int(lib().llb_attention_smem_bytes(bq, group, head_dim))
+def attention_smem_bytes(bq: int, group: int, head_dim: int, v_head_dim: Optional[int] = None) -> int:
+    return int(lib().llb_attention_smem_bytes_v(bq, group, head_dim, head_dim if v_head_dim is None else v_head_dim))
 
 
 def attention_scratch_floats(num_tiles: int, num_heads: int, head_dim: int, bq: int, nsplit: int) -> int:
+    """Floats of scratch for ``nsplit`` pieces; ``head_dim`` is the width of a VALUE row."""
     return int(lib().llb_attention_scratch_floats(num_tiles, num_heads, head_dim, bq, nsplit))
 
 
@@ -228,20 +229,141 @@ def paged_attention_simt(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
                          span_row: torch.Tensor, span_len: torch.Tensor, span_pos: torch.Tensor,
                          block_table: torch.Tensor, max_pages: int, page_size: int,
                          num_heads: int, num_kv_heads: int, head_dim: int, window: int, scale: float,
-                         bq: int, nsplit: int = 1, scratch: Optional[torch.Tensor] = None) -> None:
-    """Attention of every query row of the listed tiles over its request's pages."""
+                         bq: int, nsplit: int = 1, scratch: Optional[torch.Tensor] = None,
+                         v_head_dim: Optional[int] = None, sinks: Optional[torch.Tensor] = None) -> None:
+    """Attention of every query row of the listed tiles over its request's pages.  ``v_head_dim``: width of a value
+    row (and of an output row) when it differs from the keys'; ``v_cache`` may be ``k_cache`` itself (values read out
+    of the key rows).  ``sinks`` float32 [num_heads]: ``exp(sinks[h])`` joins head h's softmax denominator once."""
+    hdv = head_dim if v_head_dim is None else v_head_dim
     if k_cache.dtype != q.dtype or v_cache.dtype != q.dtype or out.dtype != q.dtype:
         raise KernelError("attention: q, caches and out must share a dtype")
+    if sinks is not None and (sinks.dtype != torch.float32 or sinks.numel() != num_heads):
+        raise KernelError(f"attention: sinks must be float32 [{num_heads}]")
+    if out.numel() != q.shape[0] * num_heads * hdv:
+        raise KernelError("attention: out does not fit")
     if nsplit > 1:
-        need = attention_scratch_floats(num_tiles, num_heads, head_dim, bq, nsplit)
+        need = attention_scratch_floats(num_tiles, num_heads, hdv, bq, nsplit)
         if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need:
             raise KernelError(f"attention: nsplit={nsplit} needs {need} floats of scratch")
-    _check(lib().llb_paged_attention(
+    _check(lib().llb_paged_attention_ex(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _dt(q),
         _i32(tile_span, "tile_span"), _i32(tile_q0, "tile_q0"), num_tiles,
         _i32(span_row, "span_row"), _i32(span_len, "span_len"), _i32(span_pos, "span_pos"),
-        _i32(block_table, "block_table"), max_pages, page_size, num_heads, num_kv_heads, head_dim,
+        _i32(block_table, "block_table"), max_pages, page_size, num_heads, num_kv_heads, head_dim, hdv, _ptr(sinks),
         window, ctypes.c_float(scale), bq, nsplit, _ptr(scratch), _stream()))
+
+
+def _f32(t: Optional[torch.Tensor], what: str) -> Optional[int]:
+    if t is not None and t.dtype != torch.float32:
+        raise KernelError(f"{what} must be float32, got {t.dtype}")
+    return _ptr(t)
+
+
+def layernorm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float, out: torch.Tensor,
+              rows: Optional[torch.Tensor] = None, accumulate: bool = False) -> None:
+    """out[r,:] = LN(x[rows[r],:]) * weight + bias (rows = None: row r), or out += ... with ``accumulate``.
+    x float32; weight and bias share a dtype; out float32 or bfloat16."""
+    D = x.shape[-1]
+    R = rows.numel() if rows is not None else x.numel() // D
+    if x.dtype != torch.float32 or weight.numel() != D or bias.numel() != D or weight.dtype != bias.dtype \
+            or out.numel() != R * D:
+        raise KernelError(f"layernorm: x {x.dtype} {tuple(x.shape)}, weight {tuple(weight.shape)}, out {tuple(out.shape)}")
+    _check(lib().llb_layernorm(_ptr(x), _ptr(weight), _ptr(bias), _dt(weight), _ptr(out), _dt(out), _i32(rows, "rows"),
+                               R, D, ctypes.c_float(eps), 1 if accumulate else 0, _stream()))
+
+
+GLU_SILU, GLU_CLAMPED_SWISH = 0, 1
+
+
+def glu_act(x: torch.Tensor, out: torch.Tensor, kind: int, alpha: float = 1.0, limit: float = 0.0,
+            up_shift: float = 0.0) -> None:
+    """out[m, j] = glu(x[m, 2j], x[m, 2j+1]): GLU_SILU ``silu(g) * u``; GLU_CLAMPED_SWISH
+    ``g' sigmoid(alpha g') (u' + up_shift)`` with ``g' = min(g, limit)``, ``u' = clamp(u, -limit, limit)``."""
+    M, N = x.shape
+    if N % 2 or tuple(out.shape) != (M, N // 2) or out.dtype != x.dtype:
+        raise KernelError(f"glu_act: x {tuple(x.shape)} does not fit out {tuple(out.shape)}")
+    _check(lib().llb_glu_act(_ptr(x), _ptr(out), _dt(x), M, N // 2, kind, ctypes.c_float(alpha), ctypes.c_float(limit),
+                             ctypes.c_float(up_shift), _stream()))
+
+
+def head_gate(x: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, num_heads: int, head_dim: int,
+              per_head: bool, act: str, unit_rms: bool = False, eps: float = 0.0) -> None:
+    """out[t,h,:] = (x[t,h,:], or x / rms(x) over the head with ``unit_rms``) * act(gate), act ``sigmoid`` or ``silu``.
+    ``gate`` is a [T, H] (``per_head``) or [T, H*head_dim] view whose rows may be strided (columns of a wider tensor).
+    x float32 or the dtype of gate and out."""
+    T = x.shape[0]
+    width = num_heads if per_head else num_heads * head_dim
+    if gate.dim() != 2 or tuple(gate.shape) != (T, width) or gate.stride(1) != 1 or gate.dtype != out.dtype:
+        raise KernelError(f"head_gate: gate must be {out.dtype} [{T},{width}] with unit inner stride")
+    if x.numel() != T * num_heads * head_dim or out.numel() != x.numel():
+        raise KernelError("head_gate: sizes do not fit")
+    if not gate.is_cuda:
+        raise KernelError("tensor is not on a CUDA device; there is no CPU path")
+    _check(lib().llb_head_gate(_ptr(x), _dt(x), ctypes.c_void_p(gate.data_ptr()), ctypes.c_longlong(gate.stride(0)),
+                               _ptr(out), _dt(out), T, num_heads, head_dim, 1 if unit_rms else 0, ctypes.c_float(eps),
+                               1 if per_head else 0, {"sigmoid": 0, "silu": 1}[act], _stream()))
+
+
+def qkv_prepare(src: torch.Tensor, q_off: int, k_off: int, v_off: int, num_heads: int, num_kv_heads: int,
+                head_dim: int, v_head_dim: int, positions: torch.Tensor, slot_mapping: Optional[torch.Tensor],
+                q_out: Optional[torch.Tensor], k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
+                q_norm_w: Optional[torch.Tensor] = None, k_norm_w: Optional[torch.Tensor] = None, eps: float = 0.0,
+                inv_freq: Optional[torch.Tensor] = None, rotary_dim: int = 0, interleaved: bool = False) -> None:
+    """From a fused projection ``src`` [T, C] (q at columns ``q_off``, k at ``k_off``, v at ``v_off`` or -1 for none):
+    optional RMS norm of q and of k over their whole projection, rotation, q to ``q_out`` [T, Hq*hd], k and v rows to
+    their cache slots.  ``num_heads == 0`` writes the cache only."""
+    T, C = src.shape
+    for off, n in ((q_off, num_heads * head_dim), (k_off, num_kv_heads * head_dim), (v_off, num_kv_heads * v_head_dim)):
+        if n and off >= 0 and off + n > C:
+            raise KernelError(f"qkv_prepare: columns {off}..{off + n} lie outside the {C} of src")
+    if num_heads and (q_out is None or q_out.dtype != src.dtype or q_out.numel() != T * num_heads * head_dim):
+        raise KernelError("qkv_prepare: q_out does not fit")
+    if slot_mapping is not None and num_kv_heads:
+        if k_cache is None or k_cache.dtype != src.dtype or tuple(k_cache.shape[1:]) != (num_kv_heads, head_dim):
+            raise KernelError("qkv_prepare: k_cache does not fit")
+        if v_off >= 0 and (v_cache is None or v_cache.dtype != src.dtype
+                           or tuple(v_cache.shape[1:]) != (num_kv_heads, v_head_dim)):
+            raise KernelError("qkv_prepare: v_cache does not fit")
+    if q_norm_w is not None and q_norm_w.numel() != num_heads * head_dim:
+        raise KernelError("qkv_prepare: q_norm_w must have one weight per column of q")
+    if k_norm_w is not None and k_norm_w.numel() != num_kv_heads * head_dim:
+        raise KernelError("qkv_prepare: k_norm_w must have one weight per column of k")
+    if rotary_dim and (inv_freq is None or inv_freq.numel() != rotary_dim // 2):
+        raise KernelError("qkv_prepare: inv_freq must be float32 [rotary_dim/2]")
+    _check(lib().llb_qkv_prepare(_ptr(src), _dt(src), ctypes.c_longlong(C), q_off, k_off, v_off, T, num_heads, num_kv_heads,
+                                 head_dim, v_head_dim, _f32(q_norm_w, "q_norm_w"), _f32(k_norm_w, "k_norm_w"),
+                                 ctypes.c_float(eps), _i32(positions, "positions"), _f32(inv_freq, "inv_freq"), rotary_dim,
+                                 1 if interleaved else 0, _i32(slot_mapping, "slot_mapping"), _ptr(q_out), _ptr(k_cache),
+                                 _ptr(v_cache), _stream()))
+
+
+def head_linear(x: torch.Tensor, x_off: int, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, h, :] = w[h] @ x[t, x_off + h*in : x_off + (h+1)*in] for w [H, out, in]; x [T, C], out [T, H*out]."""
+    T, C = x.shape
+    H, on, inn = w.shape
+    if x_off < 0 or x_off + H * inn > C or w.dtype != x.dtype or out.dtype != x.dtype or tuple(out.shape) != (T, H * on):
+        raise KernelError(f"head_linear: x {tuple(x.shape)} at {x_off}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    _check(lib().llb_head_linear(_ptr(x), ctypes.c_longlong(C), x_off, _ptr(w), _ptr(out), _dt(x), T, H, inn, on, _stream()))
+
+
+def retention(src: torch.Tensor, q_off: int, k_off: int, v_off: int, span_row: torch.Tensor, span_len: torch.Tensor,
+              span_pos: torch.Tensor, span_slot: torch.Tensor, num_spans: int, num_heads: int, head_dim: int,
+              v_head_dim: int, decay: torch.Tensor, inv_freq: Optional[torch.Tensor], rotary_dim: int, interleaved: bool,
+              k_scale: float, state: torch.Tensor, out: torch.Tensor) -> None:
+    """The retention recurrence over every span of the step (csrc/retention.cu): ``state`` float32
+    [slots, H, dim, vdim] is read where a span continues a request and written at its end; ``out`` float32 [T, H*vdim]."""
+    T, C = src.shape
+    if max(q_off, k_off) + num_heads * head_dim > C or v_off + num_heads * v_head_dim > C:
+        raise KernelError("retention: q, k or v lie outside the columns of src")
+    if state.dtype != torch.float32 or tuple(state.shape[1:]) != (num_heads, head_dim, v_head_dim):
+        raise KernelError(f"retention: state must be float32 [slots, {num_heads}, {head_dim}, {v_head_dim}]")
+    if out.dtype != torch.float32 or out.numel() != T * num_heads * v_head_dim or decay.numel() != num_heads:
+        raise KernelError("retention: out or decay does not fit")
+    _check(lib().llb_retention(_ptr(src), _dt(src), ctypes.c_longlong(C), q_off, k_off, v_off, _i32(span_row, "span_row"),
+                               _i32(span_len, "span_len"), _i32(span_pos, "span_pos"), _i32(span_slot, "span_slot"),
+                               num_spans, num_heads, head_dim, v_head_dim, _f32(decay, "decay"), _f32(inv_freq, "inv_freq"),
+                               rotary_dim, 1 if interleaved else 0, ctypes.c_float(k_scale), _ptr(state), _ptr(out),
+                               _stream()))
 
 
 DEPI_STORE_F32, DEPI_RESIDUAL, DEPI_SWIGLU, DEPI_ROPE_KV = 1, 2, 3, 4

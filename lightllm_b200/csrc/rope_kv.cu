@@ -109,3 +109,127 @@ LLB_EXPORT int llb_rope_table(const int* positions, const float* inv_freq, float
                                                                 transposed ? 1 : 0);
     return llb_check_launch("rope_table");
 }
+
+// ---------------------------------------------------------------------------------------------
+// The general form: q, k and v are column ranges of a wider row (a fused projection that also holds gates),
+// values may be narrower or wider than keys, and q and k may first be RMS-normalised over their WHOLE
+// projection (all heads at once, one weight per column) before the rotation:
+//     q <- q / sqrt(mean_all(q^2) + eps) * wq        (likewise k), then the rotation, then the stores.
+// Statistics, the normalised value and the rotation are float; one rounding at the store.
+// Hq == 0: only k (and v) are written; v_off < 0: no values.
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+__device__ __forceinline__ float block_sum_256(float v, float* part) {
+    v = llb_warp_sum(v);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = 0.0f;
+    for (int i = 0; i < (int)(blockDim.x >> 5); ++i) t += part[i];
+    return t;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) qkv_prepare_kernel(
+    const T* __restrict__ src, long long row_stride, int q_off, int k_off, int v_off, int Hq, int Hkv, int hd, int hdv,
+    const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w, float eps, const int* __restrict__ positions,
+    const float* __restrict__ inv_freq, int rotary_dim, int interleaved, const int* __restrict__ slot_mapping,
+    T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache) {
+    __shared__ float part[8];
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    const T* row = src + (size_t)t * row_stride;
+    const int slot = slot_mapping ? slot_mapping[t] : -1;
+    float inv_q = 1.0f, inv_k = 1.0f;
+    if (q_norm_w && Hq > 0) {
+        float ss = 0.0f;
+        for (int i = threadIdx.x; i < Hq * hd; i += blockDim.x) {
+            const float a = llb_to_float(row[q_off + i]);
+            ss += a * a;
+        }
+        inv_q = 1.0f / sqrtf(block_sum_256(ss, part) / (float)(Hq * hd) + eps);
+    }
+    if (k_norm_w && Hkv > 0) {
+        float ss = 0.0f;
+        for (int i = threadIdx.x; i < Hkv * hd; i += blockDim.x) {
+            const float a = llb_to_float(row[k_off + i]);
+            ss += a * a;
+        }
+        inv_k = 1.0f / sqrtf(block_sum_256(ss, part) / (float)(Hkv * hd) + eps);
+    }
+    const int half = rotary_dim / 2;
+    const int per_head = hd - half;
+    const int items = (Hq + Hkv) * per_head;
+    for (int it = threadIdx.x; it < items; it += blockDim.x) {
+        const int head = it / per_head;
+        const int j = it - head * per_head;
+        const bool is_q = head < Hq;
+        const int h = is_q ? head : head - Hq;
+        const T* s = row + (is_q ? q_off : k_off) + (size_t)h * hd;
+        const float* w = is_q ? q_norm_w : k_norm_w;
+        const float inv = is_q ? inv_q : inv_k;
+        T* dst;
+        if (is_q) {
+            dst = q_out + ((size_t)t * Hq + h) * hd;
+        } else {
+            if (slot < 0) continue;
+            dst = k_cache + ((size_t)slot * Hkv + h) * hd;
+        }
+        if (j < half) {
+            const int ia = interleaved ? 2 * j : j;
+            const int ib = interleaved ? 2 * j + 1 : j + half;
+            float a = llb_to_float(s[ia]), b = llb_to_float(s[ib]);
+            if (w) {
+                a = a * inv * w[h * hd + ia];
+                b = b * inv * w[h * hd + ib];
+            }
+            const float angle = (float)pos * inv_freq[j];
+            const float c = cosf(angle), sn = sinf(angle);
+            dst[ia] = llb_from_float<T>(a * c - b * sn);
+            dst[ib] = llb_from_float<T>(b * c + a * sn);
+        } else {
+            const int d = rotary_dim + (j - half);
+            float a = llb_to_float(s[d]);
+            if (w) a = a * inv * w[h * hd + d];
+            dst[d] = llb_from_float<T>(a);
+        }
+    }
+    if (slot >= 0 && v_off >= 0) {
+        const T* vsrc = row + v_off;
+        T* vdst = v_cache + (size_t)slot * Hkv * hdv;
+        for (int i = threadIdx.x; i < Hkv * hdv; i += blockDim.x) vdst[i] = vsrc[i];
+    }
+}
+
+}  // namespace
+
+// src [T, row_stride] with q at columns [q_off, q_off + Hq*hd), k at [k_off, ...+Hkv*hd), v at [v_off, ...+Hkv*hdv)
+// (v_off < 0: none); q_norm_w [Hq*hd], k_norm_w [Hkv*hd] float or null; q_out [T, Hq*hd] (unused when Hq == 0);
+// k_cache [slots, Hkv, hd], v_cache [slots, Hkv, hdv]; slot_mapping [T] or null (then nothing is cached).
+LLB_EXPORT int llb_qkv_prepare(const void* src, int dtype, long long row_stride, int q_off, int k_off, int v_off, int T,
+                               int Hq, int Hkv, int hd, int hdv, const float* q_norm_w, const float* k_norm_w, float eps,
+                               const int* positions, const float* inv_freq, int rotary_dim, int interleaved,
+                               const int* slot_mapping, void* q_out, void* k_cache, void* v_cache, cudaStream_t stream) {
+    if (T == 0) return 0;
+    LLB_REQUIRE(T > 0 && Hq >= 0 && Hkv >= 0 && Hq + Hkv > 0 && hd > 0 && src && positions, "qkv_prepare: bad sizes");
+    LLB_REQUIRE(rotary_dim >= 0 && rotary_dim <= hd && rotary_dim % 2 == 0,
+                "qkv_prepare: rotary_dim %d must be even and at most head_dim %d", rotary_dim, hd);
+    LLB_REQUIRE(rotary_dim == 0 || inv_freq != nullptr, "qkv_prepare: inv_freq is null");
+    LLB_REQUIRE(Hq == 0 || q_out != nullptr, "qkv_prepare: q_out is null");
+    LLB_REQUIRE(slot_mapping == nullptr || Hkv == 0 || (k_cache != nullptr && (v_off < 0 || (v_cache != nullptr && hdv > 0))),
+                "qkv_prepare: a cache plane is missing");
+    if (dtype == LLB_F32)
+        qkv_prepare_kernel<float><<<T, 256, 0, stream>>>((const float*)src, row_stride, q_off, k_off, v_off, Hq, Hkv, hd,
+                                                         hdv, q_norm_w, k_norm_w, eps, positions, inv_freq, rotary_dim,
+                                                         interleaved, slot_mapping, (float*)q_out, (float*)k_cache,
+                                                         (float*)v_cache);
+    else if (dtype == LLB_BF16)
+        qkv_prepare_kernel<__nv_bfloat16><<<T, 256, 0, stream>>>(
+            (const __nv_bfloat16*)src, row_stride, q_off, k_off, v_off, Hq, Hkv, hd, hdv, q_norm_w, k_norm_w, eps, positions,
+            inv_freq, rotary_dim, interleaved, slot_mapping, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache,
+            (__nv_bfloat16*)v_cache);
+    else
+        return llb_fail("qkv_prepare: unknown dtype %d", dtype);
+    return llb_check_launch("qkv_prepare");
+}

@@ -3,9 +3,12 @@ from .base import CacheView, FeedForward, Mixer, Norm, Part, PositionEncoding
 from .attention import AttentionMixer
 from .block import Block, build_part
 from .embedding import LMHead, TokenEmbedding
+from .gated_attention import GatedAttentionMixer, LatentAttentionMixer
 from .mlp import GatedMLP
-from .norm import RMSNorm
+from .norm import LayerNorm, RMSNorm
+from .retention import RetentionMixer
 from .rotary import NoPositionEncoding, RotaryEmbedding
 
 __all__ = ["CacheView", "FeedForward", "Mixer", "Norm", "Part", "PositionEncoding", "AttentionMixer", "Block",
-           "build_part", "LMHead", "TokenEmbedding", "GatedMLP", "RMSNorm", "NoPositionEncoding", "RotaryEmbedding"]
+           "build_part", "LMHead", "TokenEmbedding", "GatedMLP", "RMSNorm", "LayerNorm", "GatedAttentionMixer",
+           "LatentAttentionMixer", "RetentionMixer", "NoPositionEncoding", "RotaryEmbedding"]

@@ -47,12 +47,20 @@ class AttentionMixer(Mixer):
     def __init__(self, prefix: str, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position: Optional[PartSpec] = None, qkv_bias: bool = True, out_bias: bool = False,
                  window: Optional[int] = None, scale: Optional[float] = None,
-                 names: Optional[Dict[str, str]] = None):
+                 names: Optional[Dict[str, str]] = None, weight_suffix: str = ".weight",
+                 v_head_dim: Optional[int] = None):
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} query heads are not a multiple of {num_kv_heads} kv heads")
         self.prefix = prefix
         self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim = hidden_size, num_heads, num_kv_heads, head_dim
         self.qkv_bias, self.out_bias = qkv_bias, out_bias
+        # Values may be narrower or wider than keys; ``sinks`` (float32 [heads], set by mixers that have them) adds
+        # exp(sink_h) to each head's softmax denominator; ``values_in_keys``: the cache keeps no value rows and the
+        # kernels read the values out of the key rows.  Any of these takes the CUDA-core attention kernels.
+        self.v_head_dim = head_dim if v_head_dim is None else int(v_head_dim)
+        self.sinks: Optional[torch.Tensor] = None
+        self.values_in_keys = False
+        self.weight_suffix = weight_suffix
         self.window = window
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
         self.names = {"q": "q_proj", "k": "k_proj", "v": "v_proj", "o": "o_proj"}
@@ -62,16 +70,21 @@ class AttentionMixer(Mixer):
         self.w_qkv = self.b_qkv = self.w_o = self.b_o = None
 
     def _n(self, which: str, what: str) -> str:
-        return f"{self.prefix}.{self.names[which]}.{what}"
+        """Checkpoint name: ``<prefix>.<projection><weight_suffix>`` for a weight, ``<prefix>.<projection>.<what>`` else."""
+        base = f"{self.prefix}.{self.names[which]}"
+        return base + self.weight_suffix if what == "weight" else f"{base}.{what}"
 
     def children(self):
         return [self.position]
 
     def cache_spec(self) -> CacheSpec:
-        return CacheSpec(kv=KVSpec(self.num_kv_heads, self.head_dim, self.window))
+        vd = 0 if self.values_in_keys else (None if self.v_head_dim == self.head_dim else self.v_head_dim)
+        return CacheSpec(kv=KVSpec(self.num_kv_heads, self.head_dim, self.window, vd))
 
     def weight_specs(self) -> List[WeightSpec]:
         D, hq, hkv = self.hidden_size, self.num_heads * self.head_dim, self.num_kv_heads * self.head_dim
+        if self.v_head_dim != self.head_dim:
+            raise NotImplementedError("values of another width than the keys need a mixer that projects them so")
         specs = [WeightSpec(self._n("q", "weight"), (hq, D)), WeightSpec(self._n("k", "weight"), (hkv, D)),
                  WeightSpec(self._n("v", "weight"), (hkv, D)), WeightSpec(self._n("o", "weight"), (D, hq))]
         if self.qkv_bias:
@@ -185,7 +198,7 @@ class AttentionMixer(Mixer):
     def tile_height(self) -> int:
         group = self.num_heads // self.num_kv_heads
         for bq in (16, 8, 4, 2, 1):
-            need = ops.attention_smem_bytes(bq, group, self.head_dim)
+            need = ops.attention_smem_bytes(bq, group, self.head_dim, self.v_head_dim)
             if need <= _SMEM_BUDGET or (bq == 1 and need <= _SMEM_LIMIT):
                 return bq
         raise ops.KernelError(
@@ -196,11 +209,12 @@ class AttentionMixer(Mixer):
         """Which kernels this step's attention takes and over which tiles: made once per step (in
         ``prepare`` when the engine runs it, so that the index arrays travel with the step's metadata)."""
         window = self.window or 0
-        key = ("attention_plan", self.num_heads, self.num_kv_heads, self.head_dim, window, dtype)
+        plain = self.v_head_dim == self.head_dim and self.sinks is None and not self.values_in_keys
+        key = ("attention_plan", self.num_heads, self.num_kv_heads, self.head_dim, window, dtype, plain)
         plan = ctx.memo.get(key)
         if plan is not None:
             return plan
-        bf16 = dtype == torch.bfloat16
+        bf16 = dtype == torch.bfloat16 and plain          # the tensor-core kernels take the plain form only
         if ctx.decode_only:
             S = ctx.num_spans
             bound = ctx.max_pages * ctx.page_size          # the same for every step of this shape
@@ -270,7 +284,8 @@ class AttentionMixer(Mixer):
             pos_key = getattr(self.position, "prepare_key", None)
             if pos_key is None:
                 return None
-        return ("attention", self.num_heads, self.num_kv_heads, self.head_dim, self.window or 0, pos_key)
+        return ("attention", self.num_heads, self.num_kv_heads, self.head_dim, self.v_head_dim, self.window or 0,
+                self.sinks is not None, self.values_in_keys, pos_key)
 
     def prepare(self, ctx, cache=None) -> None:
         self._plan(ctx, ctx.dtype)
@@ -284,6 +299,8 @@ class AttentionMixer(Mixer):
         common = (ctx.span_row, ctx.span_len, ctx.span_pos, ctx.block_tables[g], ctx.max_pages, ctx.page_size,
                   self.num_heads, self.num_kv_heads, self.head_dim, window, self.scale)
         plan = self._plan(ctx, q.dtype)
+        if cache.v is None and not self.values_in_keys:
+            raise ops.KernelError("attention: the cache plane keeps no values")
         if plan[0] == "decode_mma":
             (tile_span, tile_q0, ntiles), nsplit = plan[1], plan[2]
             scratch = None
@@ -312,9 +329,10 @@ class AttentionMixer(Mixer):
         tile_span, tile_q0, ntiles = tiles
         scratch = None
         if nsplit > 1:
-            scratch = torch.empty(ops.attention_scratch_floats(ntiles, self.num_heads, self.head_dim, bq, nsplit),
+            scratch = torch.empty(ops.attention_scratch_floats(ntiles, self.num_heads, self.v_head_dim, bq, nsplit),
                                   dtype=torch.float32, device=q.device)
-        ops.paged_attention_simt(q, cache.k, cache.v, out, tile_span, tile_q0, ntiles, *common, bq, nsplit, scratch)
+        ops.paged_attention_simt(q, cache.k, cache.k if self.values_in_keys else cache.v, out, tile_span, tile_q0, ntiles,
+                                 *common, bq, nsplit, scratch, v_head_dim=self.v_head_dim, sinks=self.sinks)
 
 
 register_part("mixer", "attention", AttentionMixer)

@@ -71,7 +71,9 @@ class Block(Part):
             sb.part.forward(x, target, ctx, cache)
         else:
             sb.part.forward(x, target, ctx)
-        if branch:
+        if branch and hasattr(sb.norm_after, "add_into"):
+            sb.norm_after.add_into(target, residual, ctx)          # one kernel, the sum in float32
+        elif branch:
             ops.cast_add(sb.norm_after.forward(target, ctx), residual, accumulate=True)
         elif sb.norm_after is not None:
             ops.cast_add(sb.norm_after.forward(residual, ctx), residual)

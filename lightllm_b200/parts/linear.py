@@ -119,6 +119,15 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
     return out
 
 
+def linear_glu(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], kind: int, alpha: float, limit: float,
+               up_shift: float) -> torch.Tensor:
+    """``glu(x @ W^T)`` on interleaved (gate, up) rows of ``w`` with the activation ``kind`` of ``ops.glu_act``."""
+    pre = linear(x, w, bias, STORE)
+    out = torch.empty((x.shape[0], w.shape[0] // 2), dtype=x.dtype, device=x.device)
+    ops.glu_act(pre, out, kind, alpha, limit, up_shift)
+    return out
+
+
 def linear_normed(lazy, w: torch.Tensor, bias: Optional[torch.Tensor], epilogue: int) -> torch.Tensor:
     """``linear`` on a LazyNorm input: the norm runs inside the contraction when the shape allows."""
     M, N = lazy.num_rows, w.shape[0]

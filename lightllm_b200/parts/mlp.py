@@ -11,9 +11,15 @@ from . import linear as L
 from .base import FeedForward, LazyNorm
 
 
+# activation name -> the kernels' code
+ACTIVATIONS = {"silu": 0, "clamped_swish": 1}
+
+
 class GatedMLP(FeedForward):
-    """SwiGLU: ``h += (silu(x Wg^T) * (x Wu^T)) Wd^T``
-    (src/engine/engine_server.cpp:1875-1880, SiLU as src/ops/elementwise.cu:27-33).
+    """A gated feed-forward ``h += act(x Wg^T, x Wu^T) Wd^T``.
+
+    ``silu``: SwiGLU, ``silu(g) * u`` (src/engine/engine_server.cpp:1875-1880, SiLU as src/ops/elementwise.cu:27-33).
+    ``clamped_swish``: ``g' = min(g, limit)``, ``u' = clamp(u, -limit, limit)``, ``g' * sigmoid(alpha * g') * (u' + up_shift)``.
 
     The gate and up matrices are interleaved row by row at load time, so that one contraction
     produces each (gate, up) pair in adjacent columns and the epilogue writes only
@@ -22,16 +28,22 @@ class GatedMLP(FeedForward):
     graph_safe = True
 
     def __init__(self, prefix: str, hidden_size: int, intermediate_size: int, activation: str = "silu",
-                 bias: bool = False, names: Optional[Dict[str, str]] = None):
-        if activation != "silu":
-            raise ValueError(f"the gated feed-forward implements 'silu', not {activation!r}")
+                 bias: bool = False, names: Optional[Dict[str, str]] = None, weight_suffix: str = ".weight",
+                 alpha: float = 1.0, limit: Optional[float] = None, up_shift: float = 0.0):
+        if activation not in ACTIVATIONS:
+            raise ValueError(f"the gated feed-forward implements {sorted(ACTIVATIONS)}, not {activation!r}")
+        if activation == "clamped_swish" and (limit is None or not limit > 0):
+            raise ValueError("the clamped gate needs a positive 'limit'")
         self.prefix, self.hidden_size, self.intermediate_size, self.bias = prefix, hidden_size, intermediate_size, bias
+        self.activation, self.alpha, self.limit, self.up_shift = activation, float(alpha), float(limit or 0.0), float(up_shift)
         self.names = {"gate": "gate_proj", "up": "up_proj", "down": "down_proj"}
         self.names.update(names or {})
+        self.weight_suffix = weight_suffix
         self.w_gate_up = self.b_gate_up = self.w_down = self.b_down = None
 
     def _n(self, which: str, what: str) -> str:
-        return f"{self.prefix}.{self.names[which]}.{what}"
+        base = f"{self.prefix}.{self.names[which]}"
+        return base + self.weight_suffix if what == "weight" else f"{base}.{what}"
 
     def weight_specs(self) -> List[WeightSpec]:
         D, I = self.hidden_size, self.intermediate_size
@@ -57,6 +69,13 @@ class GatedMLP(FeedForward):
     accepts_lazy_norm = True
 
     def forward(self, x, residual, ctx=None) -> None:
+        if self.activation != "silu":
+            if isinstance(x, LazyNorm):
+                x = x.materialize()
+            act = L.linear_glu(x, self.w_gate_up, self.b_gate_up, ACTIVATIONS[self.activation], self.alpha, self.limit,
+                               self.up_shift)
+            L.linear(act, self.w_down, self.b_down, L.RESIDUAL, residual=residual)
+            return
         if isinstance(x, LazyNorm):
             act = L.linear_normed(x, self.w_gate_up, self.b_gate_up, L.SWIGLU)
         else:

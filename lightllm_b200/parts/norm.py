@@ -46,4 +46,46 @@ class RMSNorm(Norm):
         return out
 
 
+class LayerNorm(Norm):
+    """``y = (x - mean) / sqrt(var + eps) * weight + bias`` with ``var`` the mean of the squared deviations, all in
+    float32.  ``weight_name`` / ``bias_name`` are appended to ``prefix`` with a dot; an empty ``weight_name`` makes the
+    prefix itself the weight's name.  As a norm on a branch's output (``h += LN(branch)``) the sum is one kernel and
+    stays float32 (:meth:`add_into`)."""
+
+    graph_safe = True
+
+    def __init__(self, prefix: str, hidden_size: int, eps: float, weight_name: str = "weight", bias_name: str = "bias"):
+        join = lambda tail: f"{prefix}.{tail}" if prefix and tail else (prefix or tail)
+        self.name, self.bias_name = join(weight_name), join(bias_name)
+        self.hidden_size = hidden_size
+        self.eps = float(eps)
+        self.weight = self.bias = None
+        self.out_dtype = torch.float32
+
+    def weight_specs(self) -> List[WeightSpec]:
+        return [WeightSpec(self.name, (self.hidden_size,), init=("one_plus_normal", 0.1)),
+                WeightSpec(self.bias_name, (self.hidden_size,), init=("normal", 0.1))]
+
+    def bind(self, tensors: Dict[str, torch.Tensor], dtype, device) -> None:
+        self.weight, self.bias = tensors[self.name], tensors[self.bias_name]
+        if self.weight.dtype != self.bias.dtype:
+            self.weight, self.bias = self.weight.float(), self.bias.float()
+        self.out_dtype = dtype
+
+    def forward(self, residual, ctx=None):
+        out = torch.empty(residual.shape, dtype=self.out_dtype, device=residual.device)
+        ops.layernorm(residual, self.weight, self.bias, self.eps, out)
+        return out
+
+    def forward_rows(self, residual, rows, ctx=None):
+        out = torch.empty((rows.numel(), self.hidden_size), dtype=self.out_dtype, device=residual.device)
+        ops.layernorm(residual, self.weight, self.bias, self.eps, out, rows=rows)
+        return out
+
+    def add_into(self, branch, residual, ctx=None) -> None:
+        """``residual += LN(branch)``, both float32: the normed branch is never rounded to the compute dtype."""
+        ops.layernorm(branch, self.weight, self.bias, self.eps, residual, accumulate=True)
+
+
 register_part("norm", "rmsnorm", RMSNorm)
+register_part("norm", "layernorm", LayerNorm)
