@@ -248,7 +248,9 @@ class ModelRunner:
         # one view per field, cut in one call (a slice each costs the host a microsecond or more)
         (map_rows_dev, map_from_dev, ctx.span_row, ctx.span_len, ctx.span_pos, ctx.span_slot, ctx.iota, ctx.zeros, tables,
          ctx.want_rows, ctx.token_ids, ctx.positions, slots) = d[:words].split_with_sizes([n for _, n in fields])
-        if G == 1:
+        if G == 0:          # a model that keeps no pages (recurrent state only)
+            ctx.slot_mapping, ctx.block_tables = [], []
+        elif G == 1:
             ctx.slot_mapping, ctx.block_tables = [slots], [tables.view(S, P)]
         else:
             ctx.slot_mapping = list(slots.split(T))

@@ -116,7 +116,8 @@ def run_trace(model_dir: str, dtype: str, trace: Trace, out_dir: str, extra_args
     done = [l for l in proc.stdout.splitlines() if l.startswith("done ")]
     assert done == [f"done {s['step']}" for s in trace.steps], proc.stdout[-2000:]
     with open(os.path.join(model_dir, "config.json")) as f:
-        vocab = json.load(f)["vocab_size"]
+        cfg = json.load(f)
+    vocab = cfg["vocab_size"] if "vocab_size" in cfg else cfg["vocab"]
     out = {}
     for n in trace.expect:
         arr = np.fromfile(os.path.join(out_dir, f"{n}.f32"), dtype="<f4")
@@ -127,15 +128,21 @@ def run_trace(model_dir: str, dtype: str, trace: Trace, out_dir: str, extra_args
     return out
 
 
+def row_rms(diff: np.ndarray) -> float:
+    """Root mean square over a row of logit differences, their mean taken off (a shift of all logits changes nothing)."""
+    d = diff.astype(np.float64)
+    return float(np.sqrt(np.mean((d - d.mean()) ** 2)))
+
+
 def compare_with_plain(trace: Trace, got: Dict[int, np.ndarray], plain_logits: Dict[str, torch.Tensor],
-                       atol: float, label: str = "") -> float:
-    """Every wanted row against the plain implementation's logits of the whole sequence.
-    On failure names the first wrong (step, request, position)."""
+                       atol: float, label: str = "", rms: bool = False) -> float:
+    """Every wanted row against the plain implementation's logits of the whole sequence: the largest difference of a
+    logit, or with ``rms`` the root mean square over the row.  On failure names the first wrong (step, request, position)."""
     worst = 0.0
     for n in sorted(trace.expect):
         for row, (rid, pos) in enumerate(trace.expect[n]):
             ref = plain_logits[rid][pos].numpy()
-            err = float(np.max(np.abs(got[n][row] - ref)))
+            err = row_rms(got[n][row] - ref) if rms else float(np.max(np.abs(got[n][row] - ref)))
             worst = max(worst, err)
             if not err <= atol:
                 raise AssertionError(
