@@ -5,6 +5,7 @@
     python bench.py --sizes 1.5b|7b          (the larger sizes of the family: a line of their own)
     python bench.py [--sizes ..] --only decode|prefill [--prompt-len N]     (one part, at another context length)
     python bench.py --only small-mixed       (the steps of a loaded server: a 16-token portion beside decoded tokens)
+    python bench.py --design kudadra [--sizes 1.5b] [--layers L]     (the Kudadra design beside Qwen2 at equal sizes)
 
 Prints one JSON line.  ``value`` is decoded tokens a second over K timed decode steps of a
 batch of 8 requests that each hold a 2,048-token prompt (random weights, random token ids),
@@ -325,6 +326,62 @@ def run_sizes(name: str, steps: int, warmup: int, layers=None, only=None) -> int
     return 0
 
 
+def kudadra_config(base: dict, layers: int, kinds=("latent_attention", "attention", "retention")) -> dict:
+    """A Kudadra model with the width, feed-forward, head count, head size and vocabulary of a Qwen2 configuration;
+    its layers cycle through ``kinds``.  The latent is 128 wide, the window 1,024 tokens."""
+    D, H, G = base["hidden_size"], base["num_attention_heads"], base["num_key_value_heads"]
+    hd = base.get("head_dim", D // H)
+    mixers = {
+        "latent_attention": {"heads": H, "dim": hd, "vdim": hd, "kv_rank": 128, "scale": hd ** -0.5},
+        "attention": {"heads": H, "kv_heads": G, "dim": hd, "vdim": hd, "mask": {"size": 1024},
+                      "rot": {"dims": hd, "base": 10000.0}, "scale": hd ** -0.5},
+        "retention": {"heads": H, "dim": hd, "vdim": hd, "decay": [1.0 - 2.0 ** (-5 - 3.0 * i / max(1, H - 1)) for i in range(H)],
+                      "rot": {"dims": hd, "base": 1000000.0}},
+    }
+    return {"architecture": "Kudadra", "vocab": base["vocab_size"], "width": D, "norm": {"eps": 1e-5},
+            "layers": [{"type": kinds[i % len(kinds)], "mixer": mixers[kinds[i % len(kinds)]],
+                        "mlp": {"kind": "dense", "ff": base["intermediate_size"], "limit": 7.0}} for i in range(layers)]}
+
+
+def run_design(name: str, sizes: str, layers: int, steps: int, warmup: int, only=None) -> int:
+    """Prefill of one 2,048-token prompt and decode at batch 1 / 8 / 64 over 2,048-token contexts for the Kudadra design:
+    all three kinds of layer in turn, each kind alone, and Qwen2 with as many layers of the same width, feed-forward,
+    heads and vocabulary.  Random weights drawn on the device; one JSON line, not the bench record."""
+    import torch
+    from lightllm_b200 import Engine
+    from lightllm_b200.models import random_model_on_device
+    base = dict(SIZES[sizes])
+    base["num_hidden_layers"] = base["max_window_layers"] = layers
+    arms = {"qwen2": base, "kudadra": kudadra_config(base, layers)}
+    for kind in ("latent_attention", "attention", "retention"):
+        arms[f"kudadra/{kind}"] = kudadra_config(base, layers, (kind,))
+    if only:
+        arms = {k: v for k, v in arms.items() if k in only.split(",")}
+    device = torch.device("cuda:0")
+    torch.cuda.set_device(device)
+    out = {"design": name, "sizes": sizes, "layers": layers, "prompt_len": PROMPT_LEN, "dtype": "bf16",
+           "data": "synthetic: random weights drawn on the device (seed 0)", "arms": {}}
+    for arm, cfg in arms.items():
+        rng = random.Random(0)
+        model = random_model_on_device(dict(cfg), 0, "bfloat16", device)
+        max_batch = 64
+        engine = Engine(None, dtype="bfloat16", max_seq_len=CONTEXT_LEN + 512, max_batch_tokens=4 * PROMPT_LEN,
+                        page_size=PAGE_SIZE, num_pages=max_batch * (PROMPT_LEN + 512) // PAGE_SIZE, max_seqs=max_batch,
+                        chunk_size=PROMPT_LEN, model=model)
+        core = engine.core
+        res = {"graphs": core.runner.use_cuda_graphs}
+        pre_ms = time_prefill(core, 5, 3, rng)
+        res["prefill"] = {"ms": round(pre_ms, 3), "tok_s": round(PROMPT_LEN * 1000.0 / pre_ms, 1)}
+        for b in (1, 8, 64):
+            ms, launches, _ = time_decode(core, b, steps, warmup, rng)
+            res[f"decode_b{b}"] = {"ms_per_step": round(ms, 4), "tok_s": round(b * 1000.0 / ms, 1), "launches": launches}
+        out["arms"][arm] = res
+        del engine, core, model
+        torch.cuda.empty_cache()
+    print(json.dumps(out))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -334,12 +391,15 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=QWEN25_05B["num_hidden_layers"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (for profiling runs)")
+    ap.add_argument("--design", choices=["kudadra"], default=None,
+                    help="measure another design beside Qwen2 at equal sizes (0.5B sizes, or --sizes; --layers, default 6; "
+                         "--only names arms, e.g. kudadra,qwen2): a line of its own, not the bench record")
     ap.add_argument("--sizes", choices=["1.5b", "7b"], default=None,
                     help="measure at the Qwen2.5-1.5B or 7B layer sizes instead (a line of its own, not the bench record)")
     ap.add_argument("--prompt-len", type=int, default=None,
                     help="tokens each request holds before decoding starts (default 2,048); with --only or --sizes, for "
                          "measurements at other context lengths, not for the bench record")
-    ap.add_argument("--only", choices=["decode", "prefill", "small-mixed"], default=None,
+    ap.add_argument("--only", default=None,
                     help="run one part only and print a short line (for profiling runs, not a bench record)")
     args = ap.parse_args()
 
@@ -352,6 +412,12 @@ def main() -> int:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     args.warmup = max(3, args.warmup)
+    if args.design:
+        return run_design(args.design, args.sizes or "0.5b", args.layers if args.layers != QWEN25_05B["num_hidden_layers"] else 6,
+                          min(args.steps, 64), args.warmup, args.only)
+    if args.only not in (None, "decode", "prefill", "small-mixed"):
+        print("bench.py: --only is decode, prefill or small-mixed")
+        return 2
     if args.prompt_len:
         if not (args.only or args.sizes) or args.prompt_len < 16:
             print("bench.py: --prompt-len goes with --only or --sizes and is at least 16")

@@ -349,9 +349,13 @@ def head_linear(x: torch.Tensor, x_off: int, w: torch.Tensor, out: torch.Tensor)
 def retention(src: torch.Tensor, q_off: int, k_off: int, v_off: int, span_row: torch.Tensor, span_len: torch.Tensor,
               span_pos: torch.Tensor, span_slot: torch.Tensor, num_spans: int, num_heads: int, head_dim: int,
               v_head_dim: int, decay: torch.Tensor, inv_freq: Optional[torch.Tensor], rotary_dim: int, interleaved: bool,
-              k_scale: float, state: torch.Tensor, out: torch.Tensor) -> None:
+              k_scale: float, state: torch.Tensor, out: torch.Tensor, pieces=None) -> None:
     """The retention recurrence over every span of the step (csrc/retention.cu): ``state`` float32
-    [slots, H, dim, vdim] is read where a span continues a request and written at its end; ``out`` float32 [T, H*vdim]."""
+    [slots, H, dim, vdim] is read where a span continues a request and written at its end; ``out`` float32 [T, H*vdim].
+
+    ``pieces = (item_span, item_c, span_first, num_items, chunk)`` cuts the spans into pieces of ``chunk`` tokens that run
+    side by side (int32 arrays on the device: the span and index of every piece, a span's pieces consecutive, and every
+    span's first piece); without it every span is one piece."""
     T, C = src.shape
     if max(q_off, k_off) + num_heads * head_dim > C or v_off + num_heads * v_head_dim > C:
         raise KernelError("retention: q, k or v lie outside the columns of src")
@@ -359,10 +363,21 @@ def retention(src: torch.Tensor, q_off: int, k_off: int, v_off: int, span_row: t
         raise KernelError(f"retention: state must be float32 [slots, {num_heads}, {head_dim}, {v_head_dim}]")
     if out.dtype != torch.float32 or out.numel() != T * num_heads * v_head_dim or decay.numel() != num_heads:
         raise KernelError("retention: out or decay does not fit")
+    scratch = None
+    if pieces is None:
+        iota = torch.arange(num_spans, dtype=torch.int32, device=src.device)
+        item_span, item_c, span_first, num_items, chunk = iota, torch.zeros_like(iota), iota, num_spans, 1 << 30
+    else:
+        item_span, item_c, span_first, num_items, chunk = pieces
+    multi = num_items > num_spans
+    if multi:
+        scratch = torch.empty((num_items, num_heads, head_dim, v_head_dim), dtype=torch.float32, device=src.device)
     _check(lib().llb_retention(_ptr(src), _dt(src), ctypes.c_longlong(C), q_off, k_off, v_off, _i32(span_row, "span_row"),
                                _i32(span_len, "span_len"), _i32(span_pos, "span_pos"), _i32(span_slot, "span_slot"),
-                               num_spans, num_heads, head_dim, v_head_dim, _f32(decay, "decay"), _f32(inv_freq, "inv_freq"),
-                               rotary_dim, 1 if interleaved else 0, ctypes.c_float(k_scale), _ptr(state), _ptr(out),
+                               num_spans, _i32(item_span, "item_span"), _i32(item_c, "item_c"),
+                               _i32(span_first, "span_first"), num_items, chunk, 1 if multi else 0, num_heads, head_dim,
+                               v_head_dim, _f32(decay, "decay"), _f32(inv_freq, "inv_freq"), rotary_dim,
+                               1 if interleaved else 0, ctypes.c_float(k_scale), _ptr(state), _ptr(scratch), _ptr(out),
                                _stream()))
 
 

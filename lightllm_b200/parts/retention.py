@@ -3,6 +3,7 @@ from __future__ import annotations
 
 from typing import Dict, List, Optional, Sequence
 
+import numpy as np
 import torch
 
 from ..cache import CacheSpec, StateSpec
@@ -70,6 +71,45 @@ class RetentionMixer(Mixer):
         self.decay = torch.tensor(self.decay_host, dtype=torch.float32, device=device)
         self.position.bind(tensors, dtype, device)
 
+    # A span longer than this is cut into pieces that run side by side (csrc/retention.cu); the pieces are made as long as
+    # the step's tokens allow while still filling the GPU with warps.
+    MIN_PIECE = 32
+    WARPS_PER_SM = 16
+
+    @property
+    def prepare_key(self):
+        return ("retention", self.num_heads, self.head_dim, self.v_head_dim)
+
+    def _pieces(self, ctx):
+        """(item_span, item_c, span_first, num_items, chunk) for this step: which pieces the spans are cut into."""
+        key = ("retention_pieces", self.num_heads, self.head_dim, self.v_head_dim)
+        hit = ctx.memo.get(key)
+        if hit is not None:
+            return hit
+        longest = max(s.length for s in ctx.spans)
+        chunk = 1 << 30
+        if longest > 2 * self.MIN_PIECE:
+            dg = 1 if self.head_dim <= 64 else 2 if self.head_dim <= 128 else 4 if self.head_dim <= 256 else 8
+            warps = self.num_heads * -(-self.v_head_dim * dg // 32)             # of one piece
+            wanted = max(1, L.num_sms(ctx.device) * self.WARPS_PER_SM // warps)   # pieces in flight
+            total = sum(s.length for s in ctx.spans)
+            chunk = max(self.MIN_PIECE, -(-(-(-total // wanted)) // 16) * 16)
+        counts = [-(-s.length // chunk) for s in ctx.spans]
+        if max(counts) == 1:
+            hit = (ctx.iota, ctx.zeros, ctx.iota, len(ctx.spans), 1 << 30)
+        else:
+            item_span = np.repeat(np.arange(len(counts), dtype=np.int32), counts)
+            first = np.concatenate([[0], np.cumsum(counts)[:-1]]).astype(np.int32)
+            item_c = (np.arange(len(item_span), dtype=np.int32) - first[item_span]).astype(np.int32)
+            items = ctx.stage(np.stack([item_span, item_c]))
+            hit = (items[0], items[1], ctx.stage(first), int(len(item_span)), int(chunk))
+        ctx.shape_key.append(("retention", hit[3], hit[4]))
+        ctx.memo[key] = hit
+        return hit
+
+    def prepare(self, ctx, cache=None) -> None:
+        self._pieces(ctx)
+
     def forward(self, x, residual, ctx, cache: CacheView) -> None:
         if isinstance(x, LazyNorm):
             x = x.materialize()
@@ -85,7 +125,7 @@ class RetentionMixer(Mixer):
         o = torch.empty((T, H * vd), dtype=torch.float32, device=x.device)
         ops.retention(fused, 0, H * hd, 2 * H * hd, ctx.span_row, ctx.span_len, ctx.span_pos, ctx.span_slot,
                       ctx.num_spans, H, hd, vd, self.decay, inv_freq, rotary_dim, interleaved, self.k_scale,
-                      cache.state, o)
+                      cache.state, o, pieces=self._pieces(ctx))
         gated = torch.empty((T, H * vd), dtype=x.dtype, device=x.device)
         g0 = 2 * H * hd + H * vd
         ops.head_gate(o, fused[:, g0: g0 + H * vd], gated, H, vd, False, self.gate_act, unit_rms=True, eps=self.norm_eps)

@@ -146,8 +146,9 @@ def plain_retention_core(q, k, v, decay, k_scale, rot, base, pos0, S0):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("chunk", [0, 5, 16])
 @pytest.mark.parametrize("H,d,e,rot", [(3, 12, 20, 8), (2, 64, 64, 64), (2, 128, 64, 64), (1, 256, 40, 0), (4, 16, 300, 16)])
-def test_retention_kernel_over_spans_and_slots(dtype, H, d, e, rot):
+def test_retention_kernel_over_spans_and_slots(dtype, H, d, e, rot, chunk):
     """Three requests in one launch: one from its first token, one that continues from a state another launch left (in
     a slot that a finished request used before), one single token; then the same sequences cut differently."""
     torch.manual_seed(d + e)
@@ -161,14 +162,21 @@ def test_retention_kernel_over_spans_and_slots(dtype, H, d, e, rot):
     state = torch.full((4, H, d, e), float("nan"), device=DEV)          # a slot's old content must never be read at position 0
 
     def run(parts):
-        """parts: (request, slot, from, to)."""
+        """parts: (request, slot, from, to).  With ``chunk`` the spans are cut into pieces of so many tokens that run
+        side by side (their contributions to the state are scanned in between)."""
         rows = torch.cat([proj[r][a:b] for r, _, a, b in parts])
         o = torch.empty(rows.shape[0], H * e, device=DEV)
         starts = np.cumsum([0] + [b - a for _, _, a, b in parts])[:-1]
         i32 = lambda xs: dev(torch.tensor(list(xs), dtype=torch.int32))
+        pieces = None
+        if chunk:
+            counts = [-(-(b - a) // chunk) for _, _, a, b in parts]
+            item_span = [i for i, n in enumerate(counts) for _ in range(n)]
+            item_c = [c for n in counts for c in range(n)]
+            pieces = (i32(item_span), i32(item_c), i32(np.cumsum([0] + counts)[:-1]), len(item_span), chunk)
         ops.retention(dev(rows), 0, H * d, 2 * H * d, i32(starts), i32(b - a for _, _, a, b in parts),
                       i32(a for _, _, a, _ in parts), i32(s for _, s, _, _ in parts), len(parts), H, d, e, dec, inv, rot,
-                      False, d ** -0.5, state, o)
+                      False, d ** -0.5, state, o, pieces=pieces)
         out, at = {}, 0
         for r, _, a, b in parts:
             out[(r, a, b)] = o[at:at + b - a].cpu()
