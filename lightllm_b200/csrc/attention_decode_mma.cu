@@ -41,7 +41,13 @@ struct DecodeParams {
     float scale_log2e;
     float* part_acc;               // [tiles, Hkv, nsplit, G, HD]
     float* part_ml;                // [tiles, Hkv, nsplit, G, 2]   (m in base-2 units, l)
+    const float* sinks;            // [Hq] or null: exp(sinks[h]) joins head h's softmax denominator once
 };
+
+// What a sink adds to a denominator whose terms are 2^(s - M): exp(sink) = 2^(sink * log2 e).
+__device__ __forceinline__ float sink_term(const float* sinks, int head, float M) {
+    return sinks ? exp2f(sinks[head] * 1.4426950408889634f - M) : 0.0f;
+}
 
 // Distributed shared memory: the float at `local_addr` (a shared-memory address of this block) in the block of
 // rank `rank` of the cluster.
@@ -285,6 +291,7 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_decode_mma_kernel(DecodePar
                 pacc[16 * HD + g * 2 + 1] = L;
             }
         } else if (p.nsplit == 1) {
+            L += sink_term(p.sinks, kvh * G + g, M);
             p.out[((size_t)row0 * p.Hq + kvh * G + g) * HD + d] = __float2bfloat16_rn(a / L);
         } else {
             p.part_acc[(base + g) * HD + d] = a;
@@ -314,6 +321,7 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_decode_mma_kernel(DecodePar
                     a += e * ld_cluster_f32(pacc_addr + (g * HD + d) * 4, sp);
                 }
             }
+            L += sink_term(p.sinks, kvh * G + g, M);
             p.out[((size_t)row0 * p.Hq + kvh * G + g) * HD + d] = __float2bfloat16_rn(a / L);
         }
         cluster_sync_all();        // no block leaves while another may still read its shared memory
@@ -342,7 +350,7 @@ __global__ void __launch_bounds__(32) decode_merge_kernel(DecodeParams p, int HD
         wsm[s] = w;
         L += w * p.part_ml[idx * 2 + 1];
     }
-    L = llb_warp_sum(L);
+    L = llb_warp_sum(L) + sink_term(p.sinks, head, M);
     __syncwarp();
     const float inv = 1.0f / L;
     for (int d = lane; d < HD; d += 32) {
@@ -477,11 +485,13 @@ LLB_EXPORT int llb_paged_decode_mma_cluster_splits() { return CLUSTER_MAX_SPLITS
 // One query row per tile: q, out [T, Hq, hd] bf16 (row = span_row[tile_span[t]] + tile_q0[t], position
 // span_pos + tile_q0); caches [slots, Hkv, hd] bf16; block_table [S, max_pages].  scratch: num_tiles * Hq *
 // nsplit * (hd + 2) floats when nsplit > llb_paged_decode_mma_cluster_splits() (fewer splits merge inside the kernel).
-LLB_EXPORT int llb_paged_decode_mma(const void* q, const void* k_cache, const void* v_cache, void* out,
-                                    const int* tile_span, const int* tile_q0, int num_tiles, const int* span_row,
-                                    const int* span_pos, const int* block_table, int max_pages, int page_size,
-                                    int Hq, int Hkv, int hd, int window, float scale, int nsplit, float* scratch,
-                                    cudaStream_t stream) {
+// sinks [Hq] float or null: exp(sinks[h]) is added once to head h's softmax denominator.  v_cache may be k_cache
+// (values read out of the key rows).
+LLB_EXPORT int llb_paged_decode_mma_sinks(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                          const int* tile_span, const int* tile_q0, int num_tiles, const int* span_row,
+                                          const int* span_pos, const int* block_table, int max_pages, int page_size,
+                                          int Hq, int Hkv, int hd, int window, float scale, int nsplit, float* scratch,
+                                          const float* sinks, cudaStream_t stream) {
     if (num_tiles == 0) return 0;
     LLB_REQUIRE(llb_paged_decode_mma_supports(Hq, Hkv, hd), "decode attention: %d/%d heads of size %d are not supported "
                 "(groups of at most 16, head size 64 or 128)", Hq, Hkv, hd);
@@ -495,9 +505,20 @@ LLB_EXPORT int llb_paged_decode_mma(const void* q, const void* k_cache, const vo
     p.out = (__nv_bfloat16*)out; p.tile_span = tile_span; p.tile_q0 = tile_q0; p.span_row = span_row; p.span_pos = span_pos;
     p.block_table = block_table; p.max_pages = max_pages; p.page_size = page_size; p.Hq = Hq; p.Hkv = Hkv;
     p.window = window; p.nsplit = nsplit; p.scale_log2e = scale * 1.4426950408889634f;
+    p.sinks = sinks;
     const int G = Hq / Hkv;
     p.part_acc = scratch;
     p.part_ml = scratch ? scratch + (size_t)num_tiles * Hkv * nsplit * G * hd : nullptr;
     if (hd == 64) return launch<64>(p, num_tiles, stream);
     return launch<128>(p, num_tiles, stream);
+}
+
+LLB_EXPORT int llb_paged_decode_mma(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                    const int* tile_span, const int* tile_q0, int num_tiles, const int* span_row,
+                                    const int* span_pos, const int* block_table, int max_pages, int page_size,
+                                    int Hq, int Hkv, int hd, int window, float scale, int nsplit, float* scratch,
+                                    cudaStream_t stream) {
+    return llb_paged_decode_mma_sinks(q, k_cache, v_cache, out, tile_span, tile_q0, num_tiles, span_row, span_pos,
+                                      block_table, max_pages, page_size, Hq, Hkv, hd, window, scale, nsplit, scratch,
+                                      nullptr, stream);
 }

@@ -116,6 +116,7 @@ struct AttnTcParams {
     float* part_o;             // [parts, Hq, 128, HD]
     float* part_ml;            // [parts, Hq, 128, 2]  (m in base-2 units, l)
     int* error_flag;
+    const float* sinks;        // [Hq] or null: exp(sinks[h]) joins head h's softmax denominator once
 };
 
 // What one work item is: 128 query rows of one span and one head over a range of key tiles.
@@ -426,7 +427,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     pm[1] = l_row;
                 }
             } else if (ok && r < it.nrows) {
-                const float inv = 1.0f / l_row;
+                // a sink is one more term of the denominator, 2^(sink * log2 e - m), without a value
+                const float sink = p.sinks ? exp2f(p.sinks[it.head] * 1.4426950408889634f - m_run) : 0.0f;
+                const float inv = 1.0f / (l_row + sink);
                 __nv_bfloat16* dst = p.out + ((size_t)(it.row0 + r) * p.Hq + it.head) * HD + half * HO;
 #pragma unroll
                 for (int d = 0; d < HO; d += 8) {
@@ -463,6 +466,7 @@ struct MergeParams {
     const int* span_len;
     const float* part_o;
     const float* part_ml;
+    const float* sinks;
     int Hq, HD;
 };
 
@@ -493,6 +497,7 @@ __global__ void __launch_bounds__(256) attention_tcgen05_merge_kernel(MergeParam
             const float4 a = *reinterpret_cast<const float4*>(p.part_o + base * HD + d);
             acc.x += w * a.x; acc.y += w * a.y; acc.z += w * a.z; acc.w += w * a.w;
         }
+        if (p.sinks) L += exp2f(p.sinks[head] * 1.4426950408889634f - M);
         const float inv = 1.0f / L;
         __nv_bfloat16* dst = p.out + ((size_t)(p.span_row[span] + q0 + r) * p.Hq + head) * HD + d;
         const __nv_bfloat162 h0 = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
@@ -564,13 +569,16 @@ LLB_EXPORT int llb_attention_tcgen05_supports(int hd, int page_size) {
 // block_table [S, max_pages].  window <= 0: every earlier key is visible.  tile_k0 / tile_nk / tile_part (or all
 // null) cut tiles into items over ranges of 128-key tiles; items with tile_part >= 0 write partial results to
 // part_scratch (num_parts * Hq * 128 * (hd + 2) floats) for llb_attention_tcgen05_merge.
-LLB_EXPORT int llb_paged_attention_tcgen05(const void* q, const void* k_cache, const void* v_cache, void* out, int T,
-                                           const int* tile_span, const int* tile_q0, int num_tiles,
-                                           const int* span_row, const int* span_len, const int* span_pos,
-                                           const int* block_table, int max_pages, int page_size, int num_slots,
-                                           int Hq, int Hkv, int hd, int window, float scale, const int* tile_k0,
-                                           const int* tile_nk, const int* tile_part, float* part_scratch,
-                                           int num_parts, int* error_flag, cudaStream_t stream) {
+// sinks [Hq] float or null: exp(sinks[h]) is added once to head h's softmax denominator (by the kernel for whole
+// tiles, by the merge for cut ones: give the merge the same pointer).  v_cache may be k_cache.
+LLB_EXPORT int llb_paged_attention_tcgen05_sinks(const void* q, const void* k_cache, const void* v_cache, void* out, int T,
+                                                 const int* tile_span, const int* tile_q0, int num_tiles,
+                                                 const int* span_row, const int* span_len, const int* span_pos,
+                                                 const int* block_table, int max_pages, int page_size, int num_slots,
+                                                 int Hq, int Hkv, int hd, int window, float scale, const int* tile_k0,
+                                                 const int* tile_nk, const int* tile_part, float* part_scratch,
+                                                 int num_parts, const float* sinks, int* error_flag,
+                                                 cudaStream_t stream) {
     if (num_tiles == 0) return 0;
     LLB_REQUIRE(tile_part == nullptr || (tile_k0 && tile_nk && (num_parts == 0 || part_scratch)),
                 "attention_tcgen05: a cut key range needs tile_k0, tile_nk, tile_part and scratch");
@@ -591,18 +599,32 @@ LLB_EXPORT int llb_paged_attention_tcgen05(const void* q, const void* k_cache, c
     p.block_table = block_table; p.max_pages = max_pages; p.page_size = page_size; p.Hq = Hq; p.Hkv = Hkv;
     p.window = window; p.num_slots = num_slots; p.scale_log2e = scale * 1.4426950408889634f; p.error_flag = error_flag;
     p.tile_k0 = tile_k0; p.tile_nk = tile_nk; p.tile_part = tile_part;
+    p.sinks = sinks;
     p.part_o = part_scratch;
     p.part_ml = part_scratch ? part_scratch + (size_t)num_parts * Hq * BQ * hd : nullptr;
     if (hd == 64) return launch<64>(mq, mk, mv, p, num_tiles, stream);
     return launch<128>(mq, mk, mv, p, num_tiles, stream);
 }
 
+LLB_EXPORT int llb_paged_attention_tcgen05(const void* q, const void* k_cache, const void* v_cache, void* out, int T,
+                                           const int* tile_span, const int* tile_q0, int num_tiles,
+                                           const int* span_row, const int* span_len, const int* span_pos,
+                                           const int* block_table, int max_pages, int page_size, int num_slots,
+                                           int Hq, int Hkv, int hd, int window, float scale, const int* tile_k0,
+                                           const int* tile_nk, const int* tile_part, float* part_scratch,
+                                           int num_parts, int* error_flag, cudaStream_t stream) {
+    return llb_paged_attention_tcgen05_sinks(q, k_cache, v_cache, out, T, tile_span, tile_q0, num_tiles, span_row, span_len,
+                                             span_pos, block_table, max_pages, page_size, num_slots, Hq, Hkv, hd, window,
+                                             scale, tile_k0, tile_nk, tile_part, part_scratch, num_parts, nullptr,
+                                             error_flag, stream);
+}
+
 // Merges the partial results of cut tiles: merge_span, merge_q0, merge_first, merge_count [num_merge] name each
 // query tile, its first part and its number of parts.
-LLB_EXPORT int llb_attention_tcgen05_merge(void* out, const int* merge_span, const int* merge_q0, const int* merge_first,
-                                           const int* merge_count, int num_merge, const int* span_row,
-                                           const int* span_len, const float* part_scratch, int num_parts, int Hq,
-                                           int hd, cudaStream_t stream) {
+LLB_EXPORT int llb_attention_tcgen05_merge_sinks(void* out, const int* merge_span, const int* merge_q0,
+                                                 const int* merge_first, const int* merge_count, int num_merge,
+                                                 const int* span_row, const int* span_len, const float* part_scratch,
+                                                 int num_parts, int Hq, int hd, const float* sinks, cudaStream_t stream) {
     if (num_merge == 0) return 0;
     LLB_REQUIRE(num_merge > 0 && part_scratch && num_parts > 0 && Hq > 0 && Hq <= 65535 && hd % 8 == 0,
                 "attention_tcgen05_merge: bad arguments");
@@ -610,6 +632,7 @@ LLB_EXPORT int llb_attention_tcgen05_merge(void* out, const int* merge_span, con
     p.out = (__nv_bfloat16*)out; p.merge_span = merge_span; p.merge_q0 = merge_q0; p.merge_first = merge_first;
     p.merge_count = merge_count; p.span_row = span_row; p.span_len = span_len; p.part_o = part_scratch;
     p.part_ml = part_scratch + (size_t)num_parts * Hq * BQ * hd; p.Hq = Hq; p.HD = hd;
+    p.sinks = sinks;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(num_merge, Hq, BQ / (256 / (hd / 4)));
     cfg.blockDim = dim3(256);
@@ -622,4 +645,12 @@ LLB_EXPORT int llb_attention_tcgen05_merge(void* out, const int* merge_span, con
     cudaError_t e = cudaLaunchKernelEx(&cfg, attention_tcgen05_merge_kernel, p);
     if (e != cudaSuccess) return llb_fail("attention_tcgen05_merge: launch failed: %s", cudaGetErrorString(e));
     return llb_check_launch("attention_tcgen05_merge");
+}
+
+LLB_EXPORT int llb_attention_tcgen05_merge(void* out, const int* merge_span, const int* merge_q0, const int* merge_first,
+                                           const int* merge_count, int num_merge, const int* span_row,
+                                           const int* span_len, const float* part_scratch, int num_parts, int Hq,
+                                           int hd, cudaStream_t stream) {
+    return llb_attention_tcgen05_merge_sinks(out, merge_span, merge_q0, merge_first, merge_count, num_merge, span_row,
+                                             span_len, part_scratch, num_parts, Hq, hd, nullptr, stream);
 }

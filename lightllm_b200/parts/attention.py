@@ -209,12 +209,13 @@ class AttentionMixer(Mixer):
         """Which kernels this step's attention takes and over which tiles: made once per step (in
         ``prepare`` when the engine runs it, so that the index arrays travel with the step's metadata)."""
         window = self.window or 0
-        plain = self.v_head_dim == self.head_dim and self.sinks is None and not self.values_in_keys
+        # the tensor-core kernels take values as wide as the keys (sinks and values in the key rows included)
+        plain = self.v_head_dim == self.head_dim
         key = ("attention_plan", self.num_heads, self.num_kv_heads, self.head_dim, window, dtype, plain)
         plan = ctx.memo.get(key)
         if plan is not None:
             return plan
-        bf16 = dtype == torch.bfloat16 and plain          # the tensor-core kernels take the plain form only
+        bf16 = dtype == torch.bfloat16 and plain
         if ctx.decode_only:
             S = ctx.num_spans
             bound = ctx.max_pages * ctx.page_size          # the same for every step of this shape
@@ -301,27 +302,29 @@ class AttentionMixer(Mixer):
         plan = self._plan(ctx, q.dtype)
         if cache.v is None and not self.values_in_keys:
             raise ops.KernelError("attention: the cache plane keeps no values")
+        v_plane = cache.k if self.values_in_keys else cache.v
         if plan[0] == "decode_mma":
             (tile_span, tile_q0, ntiles), nsplit = plan[1], plan[2]
             scratch = None
             if nsplit > ops.decode_mma_cluster_splits():
                 scratch = torch.empty(ops.attention_scratch_floats(ntiles, self.num_heads, self.head_dim, 1, nsplit),
                                       dtype=torch.float32, device=q.device)
-            ops.paged_decode_mma(q, cache.k, cache.v, out, tile_span, tile_q0, ntiles, ctx.span_row, ctx.span_pos,
+            ops.paged_decode_mma(q, cache.k, v_plane, out, tile_span, tile_q0, ntiles, ctx.span_row, ctx.span_pos,
                                  ctx.block_tables[g], ctx.max_pages, ctx.page_size, self.num_heads,
-                                 self.num_kv_heads, self.head_dim, window, self.scale, nsplit, scratch)
+                                 self.num_kv_heads, self.head_dim, window, self.scale, nsplit, scratch, sinks=self.sinks)
         elif plan[0] == "decode_simt":
             self._simt(q, cache, out, plan[1], common, 1, plan[2])
         else:
             _, items, decode, simt = plan
             if items is not None:
                 tile_span, tile_q0, ntiles, cut = items
-                ops.paged_attention_tcgen05(q, cache.k, cache.v, out, tile_span, tile_q0, ntiles, *common, cut=cut)
+                ops.paged_attention_tcgen05(q, cache.k, v_plane, out, tile_span, tile_q0, ntiles, *common, cut=cut,
+                                            sinks=self.sinks)
             if decode is not None:
                 (tile_span, tile_q0, ntiles), nsplit = decode
-                ops.paged_decode_mma(q, cache.k, cache.v, out, tile_span, tile_q0, ntiles, ctx.span_row, ctx.span_pos,
+                ops.paged_decode_mma(q, cache.k, v_plane, out, tile_span, tile_q0, ntiles, ctx.span_row, ctx.span_pos,
                                      ctx.block_tables[g], ctx.max_pages, ctx.page_size, self.num_heads,
-                                     self.num_kv_heads, self.head_dim, window, self.scale, nsplit, None)
+                                     self.num_kv_heads, self.head_dim, window, self.scale, nsplit, None, sinks=self.sinks)
             for tiles, bq, nsplit in simt:
                 self._simt(q, cache, out, tiles, common, bq, nsplit)
 

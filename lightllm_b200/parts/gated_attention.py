@@ -105,7 +105,13 @@ class LatentAttentionMixer(AttentionMixer):
     The up-projections are folded onto the query and the output (``q.k = (W_uk^T q).c`` and ``sum p v = W_uv (sum p c)``),
     so the kernels see multi-query attention with ONE kv head of width ``rank`` whose value rows are its key rows, and
     nothing of the context is ever expanded.  ``sinks``: a learned logit per head (``<prefix>.sink``) that joins the
-    softmax denominator once, without key or value and unscaled.  ``gate`` as :class:`GatedAttentionMixer`.  No positions."""
+    softmax denominator once, without key or value and unscaled.  ``gate`` as :class:`GatedAttentionMixer`.  No positions.
+
+    ``fold``: multiply the up-projections into the neighbouring matrices when the model is bound
+    (``W_q' = blockdiag(W_uk^T) W_q`` with ``heads * rank`` rows, ``W_o' = W_o blockdiag(W_uv)``; a gate of one number a
+    head commutes with ``W_uv``), so that a layer is two contractions around the attention like any other; without it
+    the two per-head contractions run as kernels of their own.  ``None`` folds when the latent is at most twice as wide
+    as a head's keys and values (the folded matrices are ``rank / head_dim`` times the size of the plain ones)."""
 
     graph_safe = True
     accepts_lazy_norm = False
@@ -113,9 +119,14 @@ class LatentAttentionMixer(AttentionMixer):
     def __init__(self, prefix: str, hidden_size: int, num_heads: int, head_dim: int, v_head_dim: int, rank: int,
                  norm_eps: float = 1e-6, scale: Optional[float] = None, window: Optional[int] = None,
                  sinks: bool = False, gate: Optional[str] = None, gate_act: str = "sigmoid",
-                 names: Optional[Dict[str, str]] = None, weight_suffix: str = ".weight"):
+                 names: Optional[Dict[str, str]] = None, weight_suffix: str = ".weight", fold: Optional[bool] = None):
         if gate not in GATES:
             raise ValueError(f"gate must be one of {GATES}, got {gate!r}")
+        if fold and gate == "elementwise":
+            raise ValueError("a gate on every element does not commute with the value up-projection: fold=False")
+        if fold is None:
+            fold = gate != "elementwise" and rank <= 2 * head_dim and rank <= 2 * v_head_dim
+        self.fold = bool(fold)
         base = {"q": "q_proj", "dkv": "kv_down", "uk": "k_up", "uv": "v_up", "o": "o_proj", "g": "g_proj", "sink": "sink"}
         base.update(names or {})
         # the attention kernels' geometry: one kv head of `rank`, values in the key rows
@@ -147,12 +158,21 @@ class LatentAttentionMixer(AttentionMixer):
         H, r = self.num_heads, self.rank
         ws = [tensors[self._n(p, "weight")] for p in ("q", "dkv") + (("g",) if self.gate is not None else ())]
         wdt = torch.float32 if any(w.dtype == torch.float32 for w in ws) else ws[0].dtype
-        self.w_fused = torch.cat([w.to(wdt) for w in ws], dim=0).contiguous()
-        # [H, rank, dim]: row o of head h is column o of that head's key up-projection
-        self.w_q_up = tensors[self._n("uk", "weight")].to(wdt).view(H, self.q_dim, r).transpose(1, 2).contiguous()
-        self.w_v_up = tensors[self._n("uv", "weight")].to(wdt).view(H, self.out_dim, r).contiguous()
-        self.c_norm_w = tensors[self._n("dkv", "norm")].float().contiguous()
+        uk = tensors[self._n("uk", "weight")].view(H, self.q_dim, r)
+        uv = tensors[self._n("uv", "weight")].view(H, self.out_dim, r)
         self.w_o = tensors[self._n("o", "weight")]
+        if self.fold:          # products in float64, rounded once to the weights' dtype
+            D = self.hidden_size
+            wq = ws[0].double().view(H, self.q_dim, D)
+            ws[0] = torch.einsum("hdr,hdk->hrk", uk.double(), wq).reshape(H * r, D)
+            wo = self.w_o.double().view(D, H, self.out_dim)
+            self.w_o = torch.einsum("khe,her->khr", wo, uv.double()).reshape(D, H * r).to(self.w_o.dtype).contiguous()
+        else:
+            # [H, rank, dim]: row o of head h is column o of that head's key up-projection
+            self.w_q_up = uk.to(wdt).transpose(1, 2).contiguous()
+            self.w_v_up = uv.to(wdt).contiguous()
+        self.w_fused = torch.cat([w.to(wdt) for w in ws], dim=0).contiguous()
+        self.c_norm_w = tensors[self._n("dkv", "norm")].float().contiguous()
         if self.has_sinks:
             self.sinks = tensors[f"{self.prefix}.{self.names['sink']}"].float().contiguous()
 
@@ -161,11 +181,25 @@ class LatentAttentionMixer(AttentionMixer):
             x = x.materialize()
         T = x.shape[0]
         H, r = self.num_heads, self.rank
-        fused = L.linear(x, self.w_fused, None, L.STORE)           # [T, H*dim | rank | gate]
-        if cache.writes:          # the normed latent goes to the cache rows of the new tokens
-            ops.qkv_prepare(fused, 0, H * self.q_dim, -1, 0, 1, r, r, ctx.positions, ctx.slot_mapping[cache.group], None,
-                            cache.k, None, None, self.c_norm_w, self.norm_eps)
+        fused = L.linear(x, self.w_fused, None, L.STORE)           # [T, q | rank | gate]
         q = torch.empty((T, H * r), dtype=x.dtype, device=x.device)
+        slots = ctx.slot_mapping[cache.group] if cache.writes else None
+        if self.fold:
+            # q is already W_uk^T q; one kernel copies it out of the fused rows and writes the normed latent to the
+            # cache rows of the new tokens
+            ops.qkv_prepare(fused, 0, H * r, -1, H, 1 if cache.writes else 0, r, r, ctx.positions, slots, q,
+                            cache.k if cache.writes else None, None, None, self.c_norm_w if cache.writes else None,
+                            self.norm_eps)
+            mixed = torch.empty((T, H * r), dtype=x.dtype, device=x.device)
+            self.attend(q, cache, ctx, mixed)                      # sum_j p_ij c_j
+            if self.gate is not None:
+                g0 = H * r + r
+                ops.head_gate(mixed, fused[:, g0: g0 + self._gate_rows()], mixed, H, r, True, self.gate_act)
+            L.linear(mixed, self.w_o, None, L.RESIDUAL, residual=residual)
+            return
+        if cache.writes:          # the normed latent goes to the cache rows of the new tokens
+            ops.qkv_prepare(fused, 0, H * self.q_dim, -1, 0, 1, r, r, ctx.positions, slots, None,
+                            cache.k, None, None, self.c_norm_w, self.norm_eps)
         ops.head_linear(fused, 0, self.w_q_up, q)                  # W_uk^T q, head by head
         mixed = torch.empty((T, H * r), dtype=x.dtype, device=x.device)
         self.attend(q, cache, ctx, mixed)                          # sum_j p_ij c_j

@@ -40,13 +40,15 @@ KUD_P = {"architecture": "Kudadra", "vocab": 301, "width": 44, "norm": {"eps": 1
     _with_mlp(_attn(3, 3, 20, 12, 40, 20), 52, 7.0),
 ]}
 # Q: the sizes the tensor-core kernels take in bfloat16 (heads of 64 and 128, a window longer than a tile), a latent of
-# 128, retention heads of 128 (two threads a column) and 256 (four).
+# 128 with narrow heads and one of 64 with heads as wide (whose up-projections the engine folds into its matrices),
+# retention heads of 128 (two threads a column) and 256 (four).
 KUD_Q = {"architecture": "Kudadra", "vocab": 517, "width": 128, "norm": {"eps": 1e-6}, "layers": [
     _with_mlp(_latent(4, 32, 48, 128), 192, 1.0),
     _with_mlp(_attn(4, 1, 64, 64, 150, 32), 192, 1.0),
     _with_mlp(_ret(2, 128, 64, [0.96875, 0.999], 64), 192, 2.0),
     _with_mlp(_attn(2, 2, 128, 128, 300, 128, base=1000000.0), None, 0),
     _with_mlp(_ret(1, 256, 32, [0.99], 0), 192, 1.0),
+    _with_mlp(_latent(3, 64, 64, 64), 192, 1.0),
 ]}
 # R: recurrent layers only (no pages at all), one head, decay 1 (nothing is ever forgotten) and a fast decay.
 KUD_R = {"architecture": "Kudadra", "vocab": 97, "width": 32, "norm": {"eps": 1e-5}, "layers": [

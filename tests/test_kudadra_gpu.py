@@ -246,6 +246,59 @@ def test_attention_kernel_with_sinks_and_value_widths(dtype, shape):
                   f"window {window}, sinks {use_sinks}", rel=None if dtype == "float32" else 1.5e-2)
 
 
+@pytest.mark.parametrize("hd", [64, 128])
+@pytest.mark.parametrize("window", [0, 200])
+def test_tensor_core_attention_with_sinks_over_values_in_the_key_rows(hd, window):
+    """The tcgen05 prefill kernel (whole key ranges and ranges cut into pieces that a second kernel merges) and the
+    mma.sync decode kernel (pieces merged in a cluster, and through scratch): one kv head whose rows are keys and
+    values at once, six query heads, sinks from negligible to dominant."""
+    torch.manual_seed(hd + window)
+    H, page, npages, n = 6, 16, 64, 700
+    pages = torch.randperm(npages)[: -(-n // page)].to(torch.int32)
+    k = torch.randn(n, 1, hd).to(torch.bfloat16)
+    kc = torch.full((npages * page, 1, hd), float("nan"), dtype=torch.bfloat16)
+    kc[pages[torch.arange(n) // page].long() * page + torch.arange(n) % page] = k
+    kc_d, bt = dev(kc), dev(pages.view(1, -1))
+    sinks = torch.tensor([-20.0, 0.0, 2.0, 4.0, 8.0, 1.0])
+    i32 = lambda *xs: dev(torch.tensor(xs, dtype=torch.int32))
+    scale = 0.5 / hd ** 0.5
+
+    def plain(q, start):
+        rows = q.shape[0]
+        want = torch.zeros(rows, H, hd, dtype=torch.float64)
+        for r in range(rows):
+            p = start + r
+            lo = max(0, p - window + 1) if window else 0
+            for h in range(H):
+                s = torch.cat([(k.double()[lo:p + 1, 0] @ q[r, h].double()) * scale, sinks[h:h + 1].double()])
+                want[r, h] = torch.softmax(s, 0)[: p + 1 - lo] @ k.double()[lo:p + 1, 0]
+        return want
+
+    for start, rows, chunk in ((0, 300, None), (380, 320, 2), (690, 10, None)):
+        q = torch.randn(rows, H, hd).to(torch.bfloat16)
+        out = torch.empty(rows, H * hd, device=DEV, dtype=torch.bfloat16)
+        # the engine's own cutting of tiles into work items
+        from lightllm_b200.engine.batch import Span, StepContext
+        ctx = StepContext()
+        ctx.spans, ctx.device = [Span("a", 0, start, rows, 0)], DEV
+        ctx.iota, ctx.zeros = i32(0), i32(0)
+        ts, tq, nt, cut = ctx.attention_items(1, window, chunk, H, 296)
+        ops.paged_attention_tcgen05(dev(q).view(rows, H * hd), kc_d, kc_d, out, ts, tq, nt, i32(0), i32(rows), i32(start),
+                                    bt, bt.shape[1], page, H, 1, hd, window, scale, cut=cut, sinks=dev(sinks))
+        ops.check_async_errors(DEV)
+        close(out.view(rows, H, hd), plain(q, start), "bfloat16", f"tcgen05, start {start}, {rows} rows, pieces of {chunk}",
+              rel=1.5e-2)
+    for nsplit in (1, 4, 20):
+        q = torch.randn(1, H, hd).to(torch.bfloat16)
+        out = torch.empty(1, H * hd, device=DEV, dtype=torch.bfloat16)
+        scratch = None
+        if nsplit > ops.decode_mma_cluster_splits():
+            scratch = torch.empty(ops.attention_scratch_floats(1, H, hd, 1, nsplit), device=DEV)
+        ops.paged_decode_mma(dev(q).view(1, H * hd), kc_d, kc_d, out, i32(0), i32(0), 1, i32(0), i32(n - 1), bt, bt.shape[1],
+                             page, H, 1, hd, window, scale, nsplit, scratch, sinks=dev(sinks))
+        close(out.view(1, H, hd), plain(q, n - 1), "bfloat16", f"decode, {nsplit} pieces", rel=1.5e-2)
+
+
 # ---------------------------------------------------------------------------------------------------------------------
 # the model through the engine
 # ---------------------------------------------------------------------------------------------------------------------
@@ -269,11 +322,58 @@ def atol_for(name, dtype, plain):
     return (FLOAT32_ATOL * max(1.0, std)) if dtype == "float32" else 2.0 * KUDADRA_BF16_WORST_REL[name] * std
 
 
-def error(got, plain, dtype) -> float:
+def row_errors(got, plain, dtype):
     d = (got.double() - plain.double())
     if dtype == "float32":
-        return float(d.abs().max())
-    return float((d - d.mean(-1, keepdim=True)).pow(2).mean(-1).sqrt().max())
+        return d.abs().max(-1).values
+    return (d - d.mean(-1, keepdim=True)).pow(2).mean(-1).sqrt()
+
+
+def error(got, plain, dtype, keep=None) -> float:
+    e = row_errors(got, plain, dtype)
+    return float(e.max() if keep is None else e[keep].max())
+
+
+def well_conditioned(toks, w, cfg, plain, tol):
+    """Rows of ``plain`` that rounding cannot move far: a row is set aside (in bfloat16 only) when multiplying every
+    matrix by 1 + 2^-9 N(0, 1), which is what storing it in bfloat16 does, already moves its logits by the whole
+    allowed error.  This happens in a sequence's first rows under a retention layer: o_0 = (q_0 . k_0) v_0 is divided by
+    its own root mean square, so a q_0 . k_0 that nearly cancels decides the SIGN of the whole row.  float32 judges
+    every row."""
+    g = torch.Generator().manual_seed(1)
+    w2 = {k: (v * (1 + 2.0 ** -9 * torch.randn(v.shape, generator=g, dtype=v.dtype)) if v.dim() == 2 else v) for k, v in w.items()}
+    moved = row_errors(K.plain_forward(toks, w2, cfg).float(), plain, "bfloat16")
+    return (moved <= tol) & ~cancelling_rows(toks, w, cfg)
+
+
+def cancelling_rows(toks, w, cfg, noise=0.02, moved=0.3):
+    """Rows at which a retention layer's normalised output hangs on a cancellation.  o_t = sum_j a_tj v_j with
+    a_tj = decay^(t-j) q_t . k_j; an error of ``noise`` (2 %: what the bfloat16 layers before it have added to the stream)
+    in q_t and k_j moves a_tj by about noise |q_t| |k_j| / sqrt(dim), and a row is set aside when that moves o_t by more
+    than ``moved`` of its own length.  In a sequence's first rows o_t has few terms (o_0 = (q_0 . k_0) v_0), and a q . k
+    that nearly cancels then decides the sign of the whole row once it is divided by its root mean square."""
+    layers = []
+    K.plain_forward(toks, w, cfg, layers_out=layers)
+    T = len(toks)
+    bad = torch.zeros(T, dtype=torch.bool)
+    x = w["embed"][torch.tensor(toks)]
+    pos = torch.arange(T)
+    for i, layer in enumerate(cfg["layers"]):
+        if layer["type"] == "retention":
+            m, W = layer["mixer"], K._sub(w, f"l{i}.mix.")
+            H, d, e = m["heads"], m["dim"], m["vdim"]
+            rot = m.get("rot") or {"dims": 0, "base": 1.0}
+            q = K.plain_rotate((x @ W["q"].T).view(T, H, d), pos, rot["dims"], rot["base"])
+            k = K.plain_rotate((x @ W["k"].T).view(T, H, d), pos, rot["dims"], rot["base"])
+            v = (x @ W["v"].T).view(T, H, e)
+            for h in range(H):
+                decay = torch.tensor(m["decay"][h], dtype=x.dtype).pow((pos[:, None] - pos[None, :]).clamp(min=0)).tril()
+                o = ((q[:, h] @ k[:, h].T) * decay) @ v[:, h]
+                da = noise * decay * q[:, h].norm(dim=-1)[:, None] * k[:, h].norm(dim=-1)[None, :] / d ** 0.5
+                do = (da.pow(2) @ v[:, h].norm(dim=-1).pow(2)).sqrt()
+                bad |= do > moved * o.norm(dim=-1)
+        x = layers[i]
+    return bad
 
 
 LENGTHS = {"P": [1, 2, 17, 33, 70, 150, 64, 49], "Q": [3, 40, 131, 330, 129, 520, 64, 257], "R": [1, 5, 40, 90, 33, 64, 17, 200],
@@ -309,7 +409,16 @@ def test_replay_all_regimes(name, dtype, tmp_path):
     once = {rid: K.plain_forward(toks, w, cfg).float() for rid, toks in seqs.items()}
     plain = {f"{regime}{rid}": lg for rid, lg in once.items() for regime in "wtpm"}
     got = run_trace(d, dtype, tr, str(tmp_path / "out"), ["--page-size", str(PAGE_SIZE[name])])
-    worst = compare_with_plain(tr, got, plain, atol_for(name, dtype, once), f"Kudadra {name} {dtype}", rms=dtype != "float32")
+    skip = None
+    if dtype != "float32":
+        skip = {}
+        for rid, toks in seqs.items():
+            ok = well_conditioned(toks, w, cfg, once[rid], atol_for(name, dtype, once))
+            for regime in "wtpm":
+                skip[f"{regime}{rid}"] = set((~ok).nonzero().flatten().tolist())
+        assert sum(len(v) for v in skip.values()) <= 0.05 * 4 * sum(len(t) for t in seqs.values())
+    worst = compare_with_plain(tr, got, plain, atol_for(name, dtype, once), f"Kudadra {name} {dtype}", rms=dtype != "float32",
+                               skip=skip)
     record(f"replay Kudadra {name} {dtype} ({len(tr.steps)} steps, pool for {tr.max_tokens} tokens)", worst, logits_std(once))
 
 
@@ -339,9 +448,10 @@ def test_sharp_attention_sees_far_keys_window_edges_and_the_sink(tmp_path, name,
     plain = K.plain_forward(toks, w, cfg).float()
     core = core_for(d, dtype, name)
     got = stepwise(core, "a", toks, [129, 2, 150 - 131, 31, 2, 64] if name == "Q" else [9, 2, 16, 38, 2, 70])
-    err = error(got, plain, dtype)
+    keep = None if dtype == "float32" else well_conditioned(toks, w, cfg, plain, atol_for(name + " sharp", dtype, plain))
+    err = error(got, plain, dtype, keep)
     record(f"sharp Kudadra {name} {dtype}", err, logits_std(plain))
-    assert err <= atol_for(name + " sharp", dtype, plain)
+    assert err <= atol_for(name + " sharp", dtype, plain) and (keep is None or keep.float().mean() > 0.95)
     core.runner.check_device_errors()
     # the plain implementation itself shows what a one-off window or a missing sink would cost here
     # (sharp scores dwarf the sinks, whose share is above rounding in float32 only; test_heavy_sinks has them large)
@@ -387,8 +497,11 @@ def test_prefill_equals_token_by_token_and_long_decoding(tmp_path, name, dtype):
     whole = stepwise(core, "a", toks, [300])
     single = stepwise(core, "b", toks, [])
     tol = atol_for(name, dtype, plain)
-    record(f"Kudadra {name} {dtype} token by token", max(error(single, plain, dtype), error(whole, plain, dtype)), logits_std(plain))
-    assert error(whole, plain, dtype) <= tol and error(single, plain, dtype) <= tol
+    keep = None if dtype == "float32" else well_conditioned(toks, w, cfg, plain, tol)
+    record(f"Kudadra {name} {dtype} token by token", max(error(single, plain, dtype, keep), error(whole, plain, dtype, keep)),
+           logits_std(plain))
+    assert error(whole, plain, dtype, keep) <= tol and error(single, plain, dtype, keep) <= tol
+    assert keep is None or keep.float().mean() > 0.95
     core.cache.check()
 
 
@@ -433,8 +546,9 @@ def test_a_batch_of_unequal_requests_equals_each_alone_and_slots_are_used_again(
     worst = 0.0
     for r in toks:
         both = torch.cat(got[r])
-        worst = max(worst, error(both, plain[r], dtype))
-        assert error(both, plain[r], dtype) <= tol, r
+        keep = None if dtype == "float32" else well_conditioned(toks[r], w, cfg, plain[r], tol)
+        worst = max(worst, error(both, plain[r], dtype, keep))
+        assert error(both, plain[r], dtype, keep) <= tol, r
         # the batch and the request alone run the same kernels on the same numbers, up to the order of split sums
         assert error(both, alone[r], dtype) <= (2e-5 if dtype == "float32" else tol), r
     record(f"Kudadra {name} {dtype} batch", worst, logits_std(plain))
