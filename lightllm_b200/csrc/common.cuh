@@ -64,4 +64,11 @@ __device__ __forceinline__ float llb_glu(float g, float u, int kind, float alpha
     return g / (1.0f + expf(-alpha * g)) * (u + up_shift);
 }
 
+// Which gated activation a contraction's GLU epilogue applies, with its constants (see llb_glu).
+struct LlbGluArgs {
+    int kind;
+    float alpha, limit, up_shift;
+};
+static inline LlbGluArgs llb_glu_silu() { return LlbGluArgs{LLB_GLU_SILU, 1.0f, 0.0f, 0.0f}; }
+
 static inline int llb_ceil_div(int a, int b) { return (a + b - 1) / b; }

@@ -58,6 +58,7 @@ struct DecodeGemmParams {
     float* acc_scratch;
     int* counters;
     int* error_flag;
+    LlbGluArgs glu;            // the gated activation of the GLU epilogue
 };
 
 // How the rotary epilogue treats one output feature n (row `row` of the block's tile): whether it is rotated, with
@@ -402,7 +403,7 @@ gemm_decode_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                                 const float other = __shfl_xor_sync(0xffffffffu, val, 1);   // gate: even rows, up: odd rows
                                 if ((lane & 1) == 0 && m < p.M && n + 1 < p.N)
                                     ((__nv_bfloat16*)p.out)[(size_t)m * (p.N / 2) + (n >> 1)] =
-                                        __float2bfloat16_rn(llb_silu(val) * other);
+                                        __float2bfloat16_rn(llb_glu(val, other, p.glu.kind, p.glu.alpha, p.glu.limit, p.glu.up_shift));
                             } else if (m < p.M && n < p.N) {
                                 const size_t idx = (size_t)m * p.N + n;
                                 if (EPI == DEPI_STORE_F32) ((float*)p.out)[idx] = val;
@@ -524,12 +525,12 @@ LLB_EXPORT int llb_gemm_decode_supports(int M, int N, int K, int norm, int epilo
 // slot_mapping only q is written and N = Hq * hd); rope_table [M, rotary_dim/2] holds (cos, sin) of each
 // token's angle (llb_rope_table).  split_k > 1 with epilogue 3 or 4 needs acc_scratch (scratch_floats >= BN * N
 // floats, all zero on entry and left zero) and counters (one int per 128 output features, zero on entry and left zero).
-LLB_EXPORT int llb_gemm_decode(const void* W, const void* a_bf16, const float* x, const int* x_rows, const void* norm_w,
-                               int norm_w_bf16, float eps, int norm, const float* bias, void* out, float* residual,
-                               int epilogue, int M, int N, int K, int split_k,
-                               const int* slot_mapping, const float* rope_table, int rotary_dim, int interleaved, int Hq,
-                               int Hkv, int hd, void* q_out, void* k_cache, void* v_cache, float* acc_scratch,
-                               long long scratch_floats, int* counters, int* error_flag, cudaStream_t stream) {
+static int gemm_decode_impl(const void* W, const void* a_bf16, const float* x, const int* x_rows, const void* norm_w,
+                            int norm_w_bf16, float eps, int norm, const float* bias, void* out, float* residual,
+                            int epilogue, int M, int N, int K, int split_k,
+                            const int* slot_mapping, const float* rope_table, int rotary_dim, int interleaved, int Hq,
+                            int Hkv, int hd, void* q_out, void* k_cache, void* v_cache, float* acc_scratch,
+                            long long scratch_floats, int* counters, int* error_flag, LlbGluArgs glu, cudaStream_t stream) {
     if (M == 0) return 0;
     LLB_REQUIRE(llb_gemm_decode_supports(M, N, K, norm, epilogue, hd), "gemm_decode: unsupported shape M=%d N=%d K=%d", M, N, K);
     LLB_REQUIRE(((uintptr_t)W % 16 == 0), "gemm_decode: weights must be 16-byte aligned");
@@ -557,6 +558,7 @@ LLB_EXPORT int llb_gemm_decode(const void* W, const void* a_bf16, const float* x
     p.q_out = (__nv_bfloat16*)q_out; p.k_cache = (__nv_bfloat16*)k_cache; p.v_cache = (__nv_bfloat16*)v_cache;
     p.acc_scratch = acc_scratch; p.counters = counters;
     p.error_flag = error_flag;
+    p.glu = glu;
     CUtensorMap mw, mx;
     int rc = cached_map(W, N, K, TILE_M, &mw);
     if (rc) return rc;
@@ -567,4 +569,26 @@ LLB_EXPORT int llb_gemm_decode(const void* W, const void* a_bf16, const float* x
     }
     if ((rc = make_map_bf16(a_bf16, M, K, BN, &mx))) return rc;
     return dispatch_bn<false>(epilogue, mw, mx, p, split_k, stream);
+}
+
+LLB_EXPORT int llb_gemm_decode(const void* W, const void* a_bf16, const float* x, const int* x_rows, const void* norm_w,
+                               int norm_w_bf16, float eps, int norm, const float* bias, void* out, float* residual,
+                               int epilogue, int M, int N, int K, int split_k,
+                               const int* slot_mapping, const float* rope_table, int rotary_dim, int interleaved, int Hq,
+                               int Hkv, int hd, void* q_out, void* k_cache, void* v_cache, float* acc_scratch,
+                               long long scratch_floats, int* counters, int* error_flag, cudaStream_t stream) {
+    return gemm_decode_impl(W, a_bf16, x, x_rows, norm_w, norm_w_bf16, eps, norm, bias, out, residual, epilogue, M, N, K,
+                            split_k, slot_mapping, rope_table, rotary_dim, interleaved, Hq, Hkv, hd, q_out, k_cache, v_cache,
+                            acc_scratch, scratch_floats, counters, error_flag, llb_glu_silu(), stream);
+}
+
+// The GLU epilogue (bf16 operand, no norm prologue) with another gated activation (LLB_GLU_*, see llb_glu).
+LLB_EXPORT int llb_gemm_decode_glu(const void* W, const void* a_bf16, const float* bias, void* out, int M, int N, int K,
+                                   int split_k, float* acc_scratch, long long scratch_floats, int* counters,
+                                   int* error_flag, int glu_kind, float glu_alpha, float glu_limit, float glu_up_shift,
+                                   cudaStream_t stream) {
+    return gemm_decode_impl(W, a_bf16, nullptr, nullptr, nullptr, 0, 0.0f, 0, bias, out, nullptr, DEPI_SWIGLU, M, N, K,
+                            split_k, nullptr, nullptr, 0, 0, 0, 0, 0, nullptr, nullptr, nullptr, acc_scratch,
+                            scratch_floats, counters, error_flag, LlbGluArgs{glu_kind, glu_alpha, glu_limit, glu_up_shift},
+                            stream);
 }

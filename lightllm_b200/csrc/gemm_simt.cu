@@ -19,7 +19,7 @@ template <typename TO, int EPI>
 struct Epilogue {
     // Called with two adjacent columns (n even) so that SwiGLU sees its gate/up pair.
     static __device__ __forceinline__ void pair(float a0, float a1, int m, int n, int N, void* out,
-                                                float* residual, bool has1) {
+                                                float* residual, bool has1, const LlbGluArgs& glu) {
         if (EPI == LLB_EPI_STORE) {
             TO* o = (TO*)out + (size_t)m * N + n;
             o[0] = llb_from_float<TO>(a0);
@@ -34,7 +34,7 @@ struct Epilogue {
             if (has1) r[1] += a1;
         } else {  // SWIGLU: column pair (2j, 2j+1) -> output column j of N/2
             TO* o = (TO*)out + (size_t)m * (N / 2) + (n >> 1);
-            o[0] = llb_from_float<TO>(llb_silu(a0) * a1);
+            o[0] = llb_from_float<TO>(llb_glu(a0, a1, glu.kind, glu.alpha, glu.limit, glu.up_shift));
         }
     }
 };
@@ -44,7 +44,8 @@ constexpr int BM = 64, BN = 64, BK = 16;
 template <typename TA, typename TW, typename TO, int EPI>
 __global__ void __launch_bounds__(256) gemm_tile_kernel(const TA* __restrict__ A, const TW* __restrict__ W,
                                                         const float* __restrict__ bias, void* __restrict__ out,
-                                                        float* __restrict__ residual, int M, int N, int K) {
+                                                        float* __restrict__ residual, int M, int N, int K,
+                                                        const LlbGluArgs glu) {
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
     const int tid = threadIdx.x;
@@ -95,7 +96,7 @@ __global__ void __launch_bounds__(256) gemm_tile_kernel(const TA* __restrict__ A
                 a0 += bias[n];
                 if (has1) a1 += bias[n + 1];
             }
-            Epilogue<TO, EPI>::pair(a0, a1, m, n, N, out, residual, has1);
+            Epilogue<TO, EPI>::pair(a0, a1, m, n, N, out, residual, has1, glu);
         }
     }
 }
@@ -105,7 +106,8 @@ __global__ void __launch_bounds__(256) gemm_tile_kernel(const TA* __restrict__ A
 template <typename TA, typename TW, typename TO, int EPI, int MAXM, int VEC>
 __global__ void __launch_bounds__(256) gemm_rows_kernel(const TA* __restrict__ A, const TW* __restrict__ W,
                                                         const float* __restrict__ bias, void* __restrict__ out,
-                                                        float* __restrict__ residual, int M, int N, int K) {
+                                                        float* __restrict__ residual, int M, int N, int K,
+                                                        const LlbGluArgs glu) {
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     const int n = warp * 2;
@@ -163,14 +165,14 @@ __global__ void __launch_bounds__(256) gemm_rows_kernel(const TA* __restrict__ A
                     a0 += bias[n];
                     if (has1) a1 += bias[n + 1];
                 }
-                Epilogue<TO, EPI>::pair(a0, a1, m, n, N, out, residual, has1);
+                Epilogue<TO, EPI>::pair(a0, a1, m, n, N, out, residual, has1, glu);
             }
         }
     }
 }
 
 template <typename TA, typename TW, typename TO, int EPI>
-int launch(const void* A, const void* W, const void* bias, void* out, float* residual, int M, int N, int K,
+int launch(const void* A, const void* W, const void* bias, void* out, float* residual, int M, int N, int K, LlbGluArgs glu,
            cudaStream_t stream) {
     const TA* a = (const TA*)A;
     const TW* w = (const TW*)W;
@@ -183,25 +185,25 @@ int launch(const void* A, const void* W, const void* bias, void* out, float* res
         constexpr int WVEC = sizeof(TW) == 2 ? 8 : 4;
         const bool aligned = (K % WVEC == 0) && ((uintptr_t)W % 16 == 0);
         if (aligned)
-            gemm_rows_kernel<TA, TW, TO, EPI, MAXM, WVEC><<<blocks, threads, 0, stream>>>(a, w, b, out, residual, M, N, K);
+            gemm_rows_kernel<TA, TW, TO, EPI, MAXM, WVEC><<<blocks, threads, 0, stream>>>(a, w, b, out, residual, M, N, K, glu);
         else
-            gemm_rows_kernel<TA, TW, TO, EPI, MAXM, 1><<<blocks, threads, 0, stream>>>(a, w, b, out, residual, M, N, K);
+            gemm_rows_kernel<TA, TW, TO, EPI, MAXM, 1><<<blocks, threads, 0, stream>>>(a, w, b, out, residual, M, N, K, glu);
         return llb_check_launch("gemm_rows");
     }
     dim3 grid(llb_ceil_div(N, BN), llb_ceil_div(M, BM));
     LLB_REQUIRE(grid.y <= 65535, "gemm: M=%d is too large for one launch", M);
-    gemm_tile_kernel<TA, TW, TO, EPI><<<grid, 256, 0, stream>>>(a, w, b, out, residual, M, N, K);
+    gemm_tile_kernel<TA, TW, TO, EPI><<<grid, 256, 0, stream>>>(a, w, b, out, residual, M, N, K, glu);
     return llb_check_launch("gemm_tile");
 }
 
 template <typename TA, typename TW>
 int dispatch_epilogue(int epi, const void* A, const void* W, const void* bias, void* out, float* residual, int M,
-                      int N, int K, cudaStream_t s) {
+                      int N, int K, LlbGluArgs glu, cudaStream_t s) {
     switch (epi) {
-        case LLB_EPI_STORE: return launch<TA, TW, TA, LLB_EPI_STORE>(A, W, bias, out, residual, M, N, K, s);
-        case LLB_EPI_STORE_F32: return launch<TA, TW, float, LLB_EPI_STORE_F32>(A, W, bias, out, residual, M, N, K, s);
-        case LLB_EPI_RESIDUAL: return launch<TA, TW, float, LLB_EPI_RESIDUAL>(A, W, bias, out, residual, M, N, K, s);
-        case LLB_EPI_SWIGLU: return launch<TA, TW, TA, LLB_EPI_SWIGLU>(A, W, bias, out, residual, M, N, K, s);
+        case LLB_EPI_STORE: return launch<TA, TW, TA, LLB_EPI_STORE>(A, W, bias, out, residual, M, N, K, glu, s);
+        case LLB_EPI_STORE_F32: return launch<TA, TW, float, LLB_EPI_STORE_F32>(A, W, bias, out, residual, M, N, K, glu, s);
+        case LLB_EPI_RESIDUAL: return launch<TA, TW, float, LLB_EPI_RESIDUAL>(A, W, bias, out, residual, M, N, K, glu, s);
+        case LLB_EPI_SWIGLU: return launch<TA, TW, TA, LLB_EPI_SWIGLU>(A, W, bias, out, residual, M, N, K, glu, s);
     }
     return llb_fail("gemm: unknown epilogue %d", epi);
 }
@@ -211,18 +213,28 @@ int dispatch_epilogue(int epi, const void* A, const void* W, const void* bias, v
 // A [M,K] (a_dtype), W [N,K] (w_dtype), bias [N] float or null.  `out` is [M,N] of a_dtype
 // (STORE), [M,N] float (STORE_F32) or [M,N/2] of a_dtype (SWIGLU, N even); `residual` is
 // [M,N] float (RESIDUAL).  Supported: (float,float), (bf16,bf16), (bf16 activations, float weights).
-LLB_EXPORT int llb_gemm_simt(const void* A, int a_dtype, const void* W, const void* bias, int w_dtype, void* out,
-                             float* residual, int epilogue, int M, int N, int K, cudaStream_t stream) {
+// glu_kind .. glu_up_shift: the gated activation of the GLU epilogue (LLB_GLU_*, see llb_glu).
+LLB_EXPORT int llb_gemm_simt_glu(const void* A, int a_dtype, const void* W, const void* bias, int w_dtype, void* out,
+                                 float* residual, int epilogue, int M, int N, int K, int glu_kind, float glu_alpha,
+                                 float glu_limit, float glu_up_shift, cudaStream_t stream) {
+    const LlbGluArgs glu = LlbGluArgs{glu_kind, glu_alpha, glu_limit, glu_up_shift};
     if (M == 0) return 0;
     LLB_REQUIRE(M > 0 && N > 0 && K > 0, "gemm: bad sizes M=%d N=%d K=%d", M, N, K);
     LLB_REQUIRE(epilogue != LLB_EPI_SWIGLU || N % 2 == 0, "gemm: SwiGLU epilogue needs an even N, got %d", N);
     LLB_REQUIRE(epilogue != LLB_EPI_RESIDUAL || residual != nullptr, "gemm: residual epilogue without residual");
     LLB_REQUIRE(epilogue == LLB_EPI_RESIDUAL || out != nullptr, "gemm: output pointer is null");
     if (a_dtype == LLB_F32 && w_dtype == LLB_F32)
-        return dispatch_epilogue<float, float>(epilogue, A, W, bias, out, residual, M, N, K, stream);
+        return dispatch_epilogue<float, float>(epilogue, A, W, bias, out, residual, M, N, K, glu, stream);
     if (a_dtype == LLB_BF16 && w_dtype == LLB_BF16)
-        return dispatch_epilogue<__nv_bfloat16, __nv_bfloat16>(epilogue, A, W, bias, out, residual, M, N, K, stream);
+        return dispatch_epilogue<__nv_bfloat16, __nv_bfloat16>(epilogue, A, W, bias, out, residual, M, N, K, glu, stream);
     if (a_dtype == LLB_BF16 && w_dtype == LLB_F32)
-        return dispatch_epilogue<__nv_bfloat16, float>(epilogue, A, W, bias, out, residual, M, N, K, stream);
+        return dispatch_epilogue<__nv_bfloat16, float>(epilogue, A, W, bias, out, residual, M, N, K, glu, stream);
     return llb_fail("gemm: unsupported dtype pair activations=%d weights=%d", a_dtype, w_dtype);
+}
+
+// The same with SiLU as the GLU epilogue's activation.
+LLB_EXPORT int llb_gemm_simt(const void* A, int a_dtype, const void* W, const void* bias, int w_dtype, void* out,
+                             float* residual, int epilogue, int M, int N, int K, cudaStream_t stream) {
+    return llb_gemm_simt_glu(A, a_dtype, W, bias, w_dtype, out, residual, epilogue, M, N, K, LLB_GLU_SILU, 1.0f, 0.0f, 0.0f,
+                             stream);
 }

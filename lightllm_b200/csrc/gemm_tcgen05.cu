@@ -32,6 +32,12 @@ using namespace t5;
 
 // SiLU for the bf16 epilogues: the fast exponential and division are far inside bf16's rounding.
 __device__ __forceinline__ float silu_fast(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
+// The GLU epilogue's activation on a (gate, up) pair: SiLU with the fast or the exact exponential, or what glu.kind names.
+template <bool FAST>
+__device__ __forceinline__ float glu_pair(const LlbGluArgs& glu, float g, float u) {
+    if (glu.kind == LLB_GLU_SILU) return (FAST ? silu_fast(g) : llb_silu(g)) * u;
+    return llb_glu(g, u, glu.kind, glu.alpha, glu.limit, glu.up_shift);
+}
 
 constexpr int TILE_M = 128;       // rows of the A role = TMEM lanes
 constexpr int TILE_K = 64;        // bf16 elements per stage row = 128 bytes = one swizzle row
@@ -53,6 +59,7 @@ struct GemmParams {
     int* counters;          // [tiles, 8] zero before and after: arrivals per warp region of a tile
     int tma_out;            // the epilogue leaves through shared memory and TMA stores (map_out is valid)
     int* error_flag;        // raised when a wait ran out of time
+    LlbGluArgs glu;         // the gated activation of the GLU epilogue
     // rotary epilogue of the q/k/v projection (heads of 64, NeoX pairs, whole head rotated)
     const float2* rope_table;   // [hd/2, M] of (cos, sin): pair-major, so that a warp's rows read neighbouring entries
     const int* slot_mapping;    // [M] cache row of each token, negative: not written
@@ -85,8 +92,8 @@ __device__ __forceinline__ void epilogue_row(const GemmParams& p, int m, int nb,
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         const __nv_bfloat162 h = __floats2bfloat162_rn(
-                            silu_fast(v[j + 4 * e]) * v[j + 4 * e + 1],
-                            silu_fast(v[j + 4 * e + 2]) * v[j + 4 * e + 3]);
+                            glu_pair<true>(p.glu, v[j + 4 * e], v[j + 4 * e + 1]),
+                            glu_pair<true>(p.glu, v[j + 4 * e + 2], v[j + 4 * e + 3]));
                         w[e] = *reinterpret_cast<const uint32_t*>(&h);
                     }
                     *reinterpret_cast<uint4*>(o + (j >> 1)) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -94,7 +101,7 @@ __device__ __forceinline__ void epilogue_row(const GemmParams& p, int m, int nb,
             } else {
 #pragma unroll
                 for (int j = 0; j < CHUNK; j += 2)
-                    if (nb + j + 1 < p.N) o[j >> 1] = __float2bfloat16_rn(llb_silu(v[j]) * v[j + 1]);
+                    if (nb + j + 1 < p.N) o[j >> 1] = __float2bfloat16_rn(glu_pair<false>(p.glu, v[j], v[j + 1]));
             }
         } else if (EPI == LLB_EPI_STORE) {
             __nv_bfloat16* o = (__nv_bfloat16*)p.out + (size_t)m * p.N + nb;
@@ -259,7 +266,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                 const float other = __shfl_xor_sync(0xffffffffu, v, 1);   // gate in even rows, up in odd
                                 if ((lane & 1) == 0 && m < p.M && n + 1 < p.N)
                                     ((__nv_bfloat16*)p.out)[(size_t)m * (p.N / 2) + (n >> 1)] =
-                                        __float2bfloat16_rn(llb_silu(v) * other);
+                                        __float2bfloat16_rn(glu_pair<false>(p.glu, v, other));
                             } else if (m < p.M && n < p.N) {
                                 const size_t idx = (size_t)m * p.N + n;
                                 if (EPI == LLB_EPI_STORE) ((__nv_bfloat16*)p.out)[idx] = __float2bfloat16_rn(v);
@@ -345,7 +352,7 @@ __device__ __forceinline__ void staged_chunk(const GemmParams& p, const CUtensor
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int j = 16 * c + 4 * e;
-                const __nv_bfloat162 h = __floats2bfloat162_rn(silu_fast(v[j]) * v[j + 1], silu_fast(v[j + 2]) * v[j + 3]);
+                const __nv_bfloat162 h = __floats2bfloat162_rn(glu_pair<true>(p.glu, v[j], v[j + 1]), glu_pair<true>(p.glu, v[j + 2], v[j + 3]));
                 w[e] = *reinterpret_cast<const uint32_t*>(&h);
             }
             *reinterpret_cast<uint4*>(row + (((piece * CHUNKS + c) ^ (lane & 7)) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -985,9 +992,11 @@ int dispatch_epi(int epi, const CUtensorMap& ma, const CUtensorMap& mb, const Ge
 // whose output row is a multiple of 16 bytes: its pieces add themselves into `residual`, float adds that commute up
 // to rounding, and the meeting place is not touched).  error_flag: one int that the kernel
 // raises if a wait inside it ran out of time (the result is then invalid), or null.
-LLB_EXPORT int llb_gemm_tcgen05(const void* A, const void* W, const float* bias, void* out, float* residual,
-                                int epilogue, int M, int N, int K, int split_k, float* partials, int* counters,
-                                int* error_flag, cudaStream_t stream) {
+// glu_kind .. glu_up_shift: the gated activation of the GLU epilogue (LLB_GLU_*, see llb_glu).
+LLB_EXPORT int llb_gemm_tcgen05_glu(const void* A, const void* W, const float* bias, void* out, float* residual,
+                                    int epilogue, int M, int N, int K, int split_k, float* partials, int* counters,
+                                    int* error_flag, int glu_kind, float glu_alpha, float glu_limit, float glu_up_shift,
+                                    cudaStream_t stream) {
     if (M == 0) return 0;
     LLB_REQUIRE(M > 0 && N > 0 && K > 0, "gemm_tcgen05: bad sizes M=%d N=%d K=%d", M, N, K);
     LLB_REQUIRE(K % 8 == 0, "gemm_tcgen05: K=%d is not a multiple of 8 (rows must be 16-byte multiples for TMA)", K);
@@ -1007,6 +1016,7 @@ LLB_EXPORT int llb_gemm_tcgen05(const void* A, const void* W, const float* bias,
     p.kb_per_split = llb_ceil_div(p.num_kb, split_k);
     split_k = llb_ceil_div(p.num_kb, p.kb_per_split);
     p.error_flag = error_flag;
+    p.glu = LlbGluArgs{glu_kind, glu_alpha, glu_limit, glu_up_shift};
     const bool swap = M <= 128;
     CUtensorMap ma, mb;
     int rc;
@@ -1041,6 +1051,14 @@ LLB_EXPORT int llb_gemm_tcgen05(const void* A, const void* W, const float* bias,
     }
     if ((rc = make_map(W, N, K, BN, &mb))) return rc;
     return dispatch_persistent<128>(epilogue, ma, mb, p, stream);
+}
+
+// The same with SiLU as the GLU epilogue's activation.
+LLB_EXPORT int llb_gemm_tcgen05(const void* A, const void* W, const float* bias, void* out, float* residual,
+                                int epilogue, int M, int N, int K, int split_k, float* partials, int* counters,
+                                int* error_flag, cudaStream_t stream) {
+    return llb_gemm_tcgen05_glu(A, W, bias, out, residual, epilogue, M, N, K, split_k, partials, counters, error_flag,
+                                LLB_GLU_SILU, 1.0f, 0.0f, 0.0f, stream);
 }
 
 // Floats of the meeting place that llb_gemm_tcgen05 needs beyond 128 rows with K cut into split_k pieces.

@@ -164,16 +164,23 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
                              _i32(rows, "rows"), R, D, ctypes.c_float(eps), _stream()))
 
 
+def _glu_args(glu):
+    """(kind, alpha, limit, up_shift) of a GLU epilogue as C arguments; ``None`` is SiLU."""
+    kind, alpha, limit, shift = glu if glu is not None else (0, 1.0, 0.0, 0.0)
+    return int(kind), ctypes.c_float(alpha), ctypes.c_float(limit), ctypes.c_float(shift)
+
+
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], epilogue: int,
-              out: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None) -> None:
-    """CUDA-core contraction a[M,K] @ w[N,K]^T with a fused epilogue (see EPI_*)."""
+              out: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None, glu=None) -> None:
+    """CUDA-core contraction a[M,K] @ w[N,K]^T with a fused epilogue (see EPI_*).  ``glu = (kind, alpha, limit,
+    up_shift)`` names the gated activation of the EPI_SWIGLU epilogue (see :func:`glu_act`; default SiLU)."""
     M, K = a.shape
     N, K2 = w.shape
     if K != K2:
         raise KernelError(f"gemm: a is {tuple(a.shape)} but w is {tuple(w.shape)}")
     _check_epilogue_args(a, N, M, bias, epilogue, out, residual)
-    _check(lib().llb_gemm_simt(_ptr(a), _dt(a), _ptr(w), _ptr(bias), _dt(w), _ptr(out), _ptr(residual),
-                               epilogue, M, N, K, _stream()))
+    _check(lib().llb_gemm_simt_glu(_ptr(a), _dt(a), _ptr(w), _ptr(bias), _dt(w), _ptr(out), _ptr(residual),
+                                   epilogue, M, N, K, *_glu_args(glu), _stream()))
 
 
 def _check_epilogue_args(a, N, M, bias, epilogue, out, residual) -> None:
@@ -475,6 +482,26 @@ def gemm_decode(w: torch.Tensor, epilogue: int, M: int, *, a: Optional[torch.Ten
         _ptr(scratch[1]) if scratch else ctypes.c_void_p(0), _ptr(async_error_flag(w.device)), _stream()))
 
 
+def gemm_decode_glu(w: torch.Tensor, a: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, split_k: int,
+                    glu) -> None:
+    """The decode contraction's GLU epilogue with the gated activation ``glu`` (as :func:`gemm_simt`): ``a`` bf16 [M, K],
+    ``w`` bf16 [N, K] with (gate, up) rows interleaved, ``out`` bf16 [M, N/2]."""
+    N, K = w.shape
+    M = a.shape[0]
+    if w.dtype != torch.bfloat16 or a.dtype != torch.bfloat16 or tuple(a.shape) != (M, K) \
+            or out.dtype != torch.bfloat16 or tuple(out.shape) != (M, N // 2):
+        raise KernelError("gemm_decode_glu: bfloat16 a [M,K], w [N,K] and out [M,N/2]")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != N):
+        raise KernelError(f"gemm_decode_glu: bias must be float32 [{N}]")
+    scratch = splitk_scratch(w.device) if split_k > 1 else None
+    if scratch is not None and scratch[1].numel() < -(-N // 128):
+        scratch = None
+    _check(lib().llb_gemm_decode_glu(
+        _ptr(w), _ptr(a), _ptr(bias), _ptr(out), M, N, K, split_k,
+        _ptr(scratch[0]) if scratch else ctypes.c_void_p(0), ctypes.c_longlong(scratch[0].numel() if scratch else 0),
+        _ptr(scratch[1]) if scratch else ctypes.c_void_p(0), _ptr(async_error_flag(w.device)), *_glu_args(glu), _stream()))
+
+
 def attention_tcgen05_supports(head_dim: int, page_size: int) -> bool:
     return bool(lib().llb_attention_tcgen05_supports(head_dim, page_size))
 
@@ -747,8 +774,8 @@ def meet_counters(device: torch.device) -> torch.Tensor:
 
 def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], epilogue: int,
                  out: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
-                 split_k: int = 1) -> None:
-    """Tensor-core contraction a[M,K] @ w[N,K]^T (bf16, K a multiple of 8) with a fused epilogue.
+                 split_k: int = 1, glu=None) -> None:
+    """Tensor-core contraction a[M,K] @ w[N,K]^T (bf16, K a multiple of 8) with a fused epilogue (``glu`` as :func:`gemm_simt`).
 
     ``split_k`` > 1 cuts K into pieces that run as separate work items: up to 128 rows for the residual
     epilogue only (atomic adds); beyond, for every epilogue, through a meeting place in which the piece that
@@ -769,8 +796,9 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
             counters = meet_counters(a.device)
             partials = torch.empty(lib().llb_gemm_tcgen05_partial_floats(M, N, split_k), dtype=torch.float32,
                                    device=a.device)
-    _check(lib().llb_gemm_tcgen05(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), _ptr(residual), epilogue, M, N, K,
-                                  split_k, _ptr(partials), _ptr(counters), _ptr(async_error_flag(a.device)), _stream()))
+    _check(lib().llb_gemm_tcgen05_glu(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), _ptr(residual), epilogue, M, N, K,
+                                      split_k, _ptr(partials), _ptr(counters), _ptr(async_error_flag(a.device)),
+                                      *_glu_args(glu), _stream()))
 
 
 def gemm_tcgen05_rope(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], rope_table: torch.Tensor,

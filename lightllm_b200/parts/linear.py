@@ -90,9 +90,10 @@ _DECODE_EPI = {STORE_F32: ops.DEPI_STORE_F32, RESIDUAL: ops.DEPI_RESIDUAL, SWIGL
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, epilogue: int = STORE,
-           out: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+           out: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None, glu=None) -> Optional[torch.Tensor]:
     """Run the contraction; returns ``out`` (allocated here when not given), or ``None`` for the
-    residual epilogue, which adds into ``residual``."""
+    residual epilogue, which adds into ``residual``.  ``glu = (kind, alpha, limit, up_shift)``: the gated activation
+    of the SWIGLU epilogue when it is not SiLU (``ops.glu_act`` has the kinds)."""
     M, N = x.shape[0], w.shape[0]
     if epilogue != RESIDUAL and out is None:
         cols = N // 2 if epilogue == SWIGLU else N
@@ -107,21 +108,29 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None
             split_k = split_k_for(M, N, x.shape[1])
         elif epilogue == SWIGLU:
             split_k = split_k_fused(M, N, x.shape[1])
-        ops.gemm_decode(w, _DECODE_EPI[epilogue], M, a=x, bias=bias, out=out, residual=residual, split_k=split_k)
+        if epilogue == SWIGLU and glu is not None:
+            ops.gemm_decode_glu(w, x, bias, out, split_k, glu)
+        else:
+            ops.gemm_decode(w, _DECODE_EPI[epilogue], M, a=x, bias=bias, out=out, residual=residual, split_k=split_k)
     elif tensor_core_eligible(x, w):
         if M > 128:
             split_k = split_k_wide(M, N, x.shape[1])
         else:
             split_k = split_k_for(M, N, x.shape[1]) if epilogue == RESIDUAL else 1
-        ops.gemm_tcgen05(x, w, bias, epilogue, out, residual, split_k)
+        ops.gemm_tcgen05(x, w, bias, epilogue, out, residual, split_k, glu=glu)
     else:
-        ops.gemm_simt(x, w, bias, epilogue, out, residual)
+        ops.gemm_simt(x, w, bias, epilogue, out, residual, glu=glu)
     return out
+
+
+FUSE_GLU = True          # False: the gated activation as a kernel of its own behind a plain contraction (for comparisons)
 
 
 def linear_glu(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], kind: int, alpha: float, limit: float,
                up_shift: float) -> torch.Tensor:
     """``glu(x @ W^T)`` on interleaved (gate, up) rows of ``w`` with the activation ``kind`` of ``ops.glu_act``."""
+    if FUSE_GLU:          # the activation in the contraction's epilogue, from the float accumulators
+        return linear(x, w, bias, SWIGLU, glu=(kind, alpha, limit, up_shift))
     pre = linear(x, w, bias, STORE)
     out = torch.empty((x.shape[0], w.shape[0] // 2), dtype=x.dtype, device=x.device)
     ops.glu_act(pre, out, kind, alpha, limit, up_shift)

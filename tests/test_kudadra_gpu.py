@@ -576,3 +576,28 @@ def test_greedy_generation_through_the_entry_point(tmp_path, name, dtype):
     eng.core.cache.check()
     assert eng.core.cache.free_slots == 3
     eng.core.runner.check_device_errors()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("M", [1, 7, 40, 130, 700])
+def test_gated_activation_in_the_contractions_epilogue(dtype, M):
+    """Every contraction kernel's GLU epilogue with the clamped gate (few rows: the decode kernel, split along K or not;
+    up to 128 rows and beyond: the two tcgen05 kernels; float32: the CUDA-core kernel) against the contraction followed
+    by the activation kernel, and against the formula."""
+    from lightllm_b200.parts import linear as L
+    torch.manual_seed(M)
+    for K_, I in ((64, 48), (896, 1216), (136, 100)):
+        x = (torch.randn(M, K_) * 0.7).to(DT[dtype])
+        w = (torch.randn(2 * I, K_) / K_ ** 0.5 * 2).to(DT[dtype])
+        pre = x.double() @ w.double().T
+        g, u = pre[:, 0::2].clamp(max=1.25), pre[:, 1::2].clamp(-1.25, 1.25)
+        want = g * torch.sigmoid(1.702 * g) * (u + 1.0)
+        args = (dev(x), dev(w), None, ops.GLU_CLAMPED_SWISH, 1.702, 1.25, 1.0)
+        fused = L.linear_glu(*args)
+        L.FUSE_GLU = False
+        try:
+            apart = L.linear_glu(*args)
+        finally:
+            L.FUSE_GLU = True
+        close(fused, want, dtype, f"fused clamped gate {M}x{K_}x{I}", rel=None if dtype == "float32" else 1e-2)
+        close(apart, want, dtype, f"clamped gate behind the contraction {M}x{K_}x{I}", rel=None if dtype == "float32" else 1.5e-2)
