@@ -494,8 +494,10 @@ def gemm_decode_glu(w: torch.Tensor, a: torch.Tensor, bias: Optional[torch.Tenso
     if bias is not None and (bias.dtype != torch.float32 or bias.numel() != N):
         raise KernelError(f"gemm_decode_glu: bias must be float32 [{N}]")
     scratch = splitk_scratch(w.device) if split_k > 1 else None
-    if scratch is not None and scratch[1].numel() < -(-N // 128):
+    if scratch is not None and (scratch[1].numel() < -(-N // 128) or scratch[0].numel() < 64 * N):
         scratch = None
+    if scratch is None:          # no meeting place was reserved for a contraction this wide: one piece
+        split_k = 1
     _check(lib().llb_gemm_decode_glu(
         _ptr(w), _ptr(a), _ptr(bias), _ptr(out), M, N, K, split_k,
         _ptr(scratch[0]) if scratch else ctypes.c_void_p(0), ctypes.c_longlong(scratch[0].numel() if scratch else 0),

@@ -51,7 +51,7 @@ struct RetParams {
 
 enum { RET_LOCAL = 1, RET_OUT = 3 };
 
-template <typename T, int NR, int DG>
+template <typename T, int NR, int DG, int MODE>
 __global__ void __launch_bounds__(256) retention_kernel(RetParams p) {
     extern __shared__ __align__(16) float sm[];
     constexpr int PADF = DG > 1 ? 4 : 0;                 // keeps the DG threads of a column on different banks
@@ -62,7 +62,7 @@ __global__ void __launch_bounds__(256) retention_kernel(RetParams p) {
     const int slen = p.span_len[span];
     const int pieces = (slen + p.chunk - 1) / p.chunk;
     const bool last = c == pieces - 1;
-    if (p.mode == RET_LOCAL && last) return;             // the last piece's contribution is never needed
+    if (MODE == RET_LOCAL && last) return;               // the last piece's contribution is never needed
     float* qs = sm;                          // [RET_STAGE][DPAD]
     float* ks = qs + RET_STAGE * DPAD;       // [RET_STAGE][DPAD]
     float* vs = ks + RET_STAGE * DPAD;       // [RET_STAGE][EV]
@@ -79,7 +79,7 @@ __global__ void __launch_bounds__(256) retention_kernel(RetParams p) {
 
     // start state: zero (local pass; a request's first token), the request's slot, or what the scan left for this piece
     const float* from = nullptr;
-    if (p.mode == RET_OUT) {
+    if (MODE == RET_OUT) {
         if (pieces > 1) from = p.scratch + ((size_t)item * p.H + h) * plane;
         else if (pos0 > 0) from = slot;
     }
@@ -106,16 +106,20 @@ __global__ void __launch_bounds__(256) retention_kernel(RetParams p) {
                 const int ib = p.interleaved ? 2 * j + 1 : j + half;
                 const float angle = (float)(pos0 + c0 + tl) * p.inv_freq[j];
                 const float cs = cosf(angle), sn = sinf(angle);
-                float a = llb_to_float(qr[ia]), b = llb_to_float(qr[ib]);
-                qs[tl * DPAD + at(ia)] = a * cs - b * sn;
-                qs[tl * DPAD + at(ib)] = b * cs + a * sn;
+                float a, b;
+                if (MODE == RET_OUT) {           // the local pass makes no outputs and needs no q
+                    a = llb_to_float(qr[ia]);
+                    b = llb_to_float(qr[ib]);
+                    qs[tl * DPAD + at(ia)] = a * cs - b * sn;
+                    qs[tl * DPAD + at(ib)] = b * cs + a * sn;
+                }
                 a = llb_to_float(kr[ia]);
                 b = llb_to_float(kr[ib]);
                 ks[tl * DPAD + at(ia)] = (a * cs - b * sn) * p.k_scale;
                 ks[tl * DPAD + at(ib)] = (b * cs + a * sn) * p.k_scale;
             } else {
                 const int d = p.rotary_dim + (j - half);
-                qs[tl * DPAD + at(d)] = llb_to_float(qr[d]);
+                if (MODE == RET_OUT) qs[tl * DPAD + at(d)] = llb_to_float(qr[d]);
                 ks[tl * DPAD + at(d)] = llb_to_float(kr[d]) * p.k_scale;
             }
         }
@@ -132,17 +136,20 @@ __global__ void __launch_bounds__(256) retention_kernel(RetParams p) {
             float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
 #pragma unroll
             for (int j = 0; j < NR; j += 4) {
-                const float4 k4 = kq[j >> 2], q4 = qq[j >> 2];
+                const float4 k4 = kq[j >> 2];
                 S[j] = fmaf(decay, S[j], k4.x * vv);
                 S[j + 1] = fmaf(decay, S[j + 1], k4.y * vv);
                 S[j + 2] = fmaf(decay, S[j + 2], k4.z * vv);
                 S[j + 3] = fmaf(decay, S[j + 3], k4.w * vv);
-                a0 = fmaf(S[j], q4.x, a0);
-                a1 = fmaf(S[j + 1], q4.y, a1);
-                a2 = fmaf(S[j + 2], q4.z, a2);
-                a3 = fmaf(S[j + 3], q4.w, a3);
+                if (MODE == RET_OUT) {
+                    const float4 q4 = qq[j >> 2];
+                    a0 = fmaf(S[j], q4.x, a0);
+                    a1 = fmaf(S[j + 1], q4.y, a1);
+                    a2 = fmaf(S[j + 2], q4.z, a2);
+                    a3 = fmaf(S[j + 3], q4.w, a3);
+                }
             }
-            if (p.mode == RET_OUT) {
+            if (MODE == RET_OUT) {
                 float acc = (a0 + a1) + (a2 + a3);
 #pragma unroll
                 for (int o = 1; o < DG; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
@@ -152,7 +159,7 @@ __global__ void __launch_bounds__(256) retention_kernel(RetParams p) {
     }
     if (!live) return;
     float* to = nullptr;
-    if (p.mode == RET_LOCAL) to = p.scratch + ((size_t)(item + 1) * p.H + h) * plane;     // the next piece's place
+    if (MODE == RET_LOCAL) to = p.scratch + ((size_t)(item + 1) * p.H + h) * plane;     // the next piece's place
     else if (last) to = slot;
     if (to != nullptr) {
 #pragma unroll
@@ -175,13 +182,24 @@ __global__ void __launch_bounds__(256) retention_scan_kernel(RetParams p) {
     const bool fresh = p.span_pos[span] == 0;
     const float step = powf(p.decay[h], (float)p.chunk);          // every piece but the last has `chunk` tokens
     const size_t first = (size_t)p.span_first[span];
+    const size_t stride = (size_t)p.H * plane;          // from one piece's place to the next
     for (size_t i = (size_t)blockIdx.z * blockDim.x + threadIdx.x; i < plane; i += (size_t)gridDim.z * blockDim.x) {
         float s = fresh ? 0.0f : slot[i];
-        p.scratch[((first)*p.H + h) * plane + i] = s;
-        for (int c = 1; c < pieces; ++c) {
-            float* a = p.scratch + ((first + c) * p.H + h) * plane + i;
-            s = fmaf(step, s, *a);
-            *a = s;
+        float* at = p.scratch + (first * p.H + h) * plane + i;
+        at[0] = s;
+        // eight pieces' contributions are requested together; only the additions wait for one another
+        for (int c = 1; c < pieces; c += 8) {
+            float a[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) a[u] = c + u < pieces ? at[(size_t)(c + u) * stride] : 0.0f;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                s = fmaf(step, s, a[u]);
+                a[u] = s;
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                if (c + u < pieces) at[(size_t)(c + u) * stride] = a[u];
         }
     }
 }
@@ -192,7 +210,8 @@ int launch_retention_as(const RetParams& p, int num_items, cudaStream_t stream) 
     dim3 grid(num_items, p.H, llb_ceil_div(p.vdim, p.EV));
     const int threads = ((p.EV * DG + 31) / 32) * 32;
     const size_t smem = ((size_t)2 * RET_STAGE * DG * (NR + PADF) + (size_t)RET_STAGE * p.EV) * sizeof(float);
-    retention_kernel<T, NR, DG><<<grid, threads, smem, stream>>>(p);
+    if (p.mode == RET_LOCAL) retention_kernel<T, NR, DG, RET_LOCAL><<<grid, threads, smem, stream>>>(p);
+    else retention_kernel<T, NR, DG, RET_OUT><<<grid, threads, smem, stream>>>(p);
     return llb_check_launch("retention");
 }
 
