@@ -267,16 +267,19 @@ def _f32(t: Optional[torch.Tensor], what: str) -> Optional[int]:
 
 
 def layernorm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float, out: torch.Tensor,
-              rows: Optional[torch.Tensor] = None, accumulate: bool = False) -> None:
+              rows: Optional[torch.Tensor] = None, accumulate: bool = False, copy: Optional[torch.Tensor] = None) -> None:
     """out[r,:] = LN(x[rows[r],:]) * weight + bias (rows = None: row r), or out += ... with ``accumulate``.
-    x float32; weight and bias share a dtype; out float32 or bfloat16."""
+    x float32; weight and bias share a dtype; out float32 or bfloat16.  ``copy`` (bfloat16, out's shape) receives what
+    was written to out as well."""
+    if copy is not None and (copy.dtype != torch.bfloat16 or copy.numel() != out.numel()):
+        raise KernelError("layernorm: copy must be bfloat16 of out's size")
     D = x.shape[-1]
     R = rows.numel() if rows is not None else x.numel() // D
     if x.dtype != torch.float32 or weight.numel() != D or bias.numel() != D or weight.dtype != bias.dtype \
             or out.numel() != R * D:
         raise KernelError(f"layernorm: x {x.dtype} {tuple(x.shape)}, weight {tuple(weight.shape)}, out {tuple(out.shape)}")
     _check(lib().llb_layernorm(_ptr(x), _ptr(weight), _ptr(bias), _dt(weight), _ptr(out), _dt(out), _i32(rows, "rows"),
-                               R, D, ctypes.c_float(eps), 1 if accumulate else 0, _stream()))
+                               R, D, ctypes.c_float(eps), 1 if accumulate else 0, _ptr(copy), _stream()))
 
 
 GLU_SILU, GLU_CLAMPED_SWISH = 0, 1

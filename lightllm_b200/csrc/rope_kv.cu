@@ -161,7 +161,8 @@ __global__ void __launch_bounds__(256) qkv_prepare_kernel(
     const int half = rotary_dim / 2;
     const int per_head = hd - half;
     const int items = (Hq + Hkv) * per_head;
-    for (int it = threadIdx.x; it < items; it += blockDim.x) {
+    // gridDim.y blocks share a token's items (each has computed the token's norms itself: they are a few KB of reads)
+    for (int it = blockIdx.y * blockDim.x + threadIdx.x; it < items; it += gridDim.y * blockDim.x) {
         const int head = it / per_head;
         const int j = it - head * per_head;
         const bool is_q = head < Hq;
@@ -198,7 +199,7 @@ __global__ void __launch_bounds__(256) qkv_prepare_kernel(
     if (slot >= 0 && v_off >= 0) {
         const T* vsrc = row + v_off;
         T* vdst = v_cache + (size_t)slot * Hkv * hdv;
-        for (int i = threadIdx.x; i < Hkv * hdv; i += blockDim.x) vdst[i] = vsrc[i];
+        for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < Hkv * hdv; i += gridDim.y * blockDim.x) vdst[i] = vsrc[i];
     }
 }
 
@@ -219,13 +220,17 @@ LLB_EXPORT int llb_qkv_prepare(const void* src, int dtype, long long row_stride,
     LLB_REQUIRE(Hq == 0 || q_out != nullptr, "qkv_prepare: q_out is null");
     LLB_REQUIRE(slot_mapping == nullptr || Hkv == 0 || (k_cache != nullptr && (v_off < 0 || (v_cache != nullptr && hdv > 0))),
                 "qkv_prepare: a cache plane is missing");
+    // few tokens (decoding): several blocks a token, so that the step's handful of rows still fills some SMs
+    const int per_token = (Hq + Hkv) * (hd - rotary_dim / 2);
+    const int share = T >= 256 ? 1 : (per_token + 255) / 256 < 8 ? (per_token + 255) / 256 : 8;
+    const dim3 grid(T, share < 1 ? 1 : share);
     if (dtype == LLB_F32)
-        qkv_prepare_kernel<float><<<T, 256, 0, stream>>>((const float*)src, row_stride, q_off, k_off, v_off, Hq, Hkv, hd,
+        qkv_prepare_kernel<float><<<grid, 256, 0, stream>>>((const float*)src, row_stride, q_off, k_off, v_off, Hq, Hkv, hd,
                                                          hdv, q_norm_w, k_norm_w, eps, positions, inv_freq, rotary_dim,
                                                          interleaved, slot_mapping, (float*)q_out, (float*)k_cache,
                                                          (float*)v_cache);
     else if (dtype == LLB_BF16)
-        qkv_prepare_kernel<__nv_bfloat16><<<T, 256, 0, stream>>>(
+        qkv_prepare_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(
             (const __nv_bfloat16*)src, row_stride, q_off, k_off, v_off, Hq, Hkv, hd, hdv, q_norm_w, k_norm_w, eps, positions,
             inv_freq, rotary_dim, interleaved, slot_mapping, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache,
             (__nv_bfloat16*)v_cache);

@@ -10,6 +10,9 @@ from ..csrc import ops
 from .base import LazyNorm, Part
 
 
+_STREAM_COPY = "stream in the compute dtype"      # ctx.memo key: (the stream tensor, its copy), valid until the stream changes
+
+
 def build_part(role: str, spec):
     return part_class(role, spec.kind)(spec.prefix, **spec.params)
 
@@ -52,6 +55,9 @@ class Block(Part):
             dtype = ctx.dtype if ctx is not None and ctx.dtype is not None else residual.dtype
             if dtype == residual.dtype:
                 return residual
+            ready = ctx.memo.pop(_STREAM_COPY, None) if ctx is not None else None
+            if ready is not None and ready[0] is residual and ready[1].dtype == dtype:
+                return ready[1]          # the kernel that last wrote the stream left it in the compute dtype too
             x = torch.empty(residual.shape, dtype=dtype, device=residual.device)
             ops.cast_add(residual, x)
             return x
@@ -62,6 +68,8 @@ class Block(Part):
     @staticmethod
     def _run(sb: BuiltSubBlock, x, residual, ctx, cache) -> None:
         branch = sb.norm_after is not None and sb.after == "branch"
+        if ctx is not None:
+            ctx.memo.pop(_STREAM_COPY, None)          # the stream is about to change
         target = residual
         if branch:      # the part adds into a cleared buffer, which is normed and then added to the stream
             target = torch.zeros_like(residual)
@@ -72,7 +80,16 @@ class Block(Part):
         else:
             sb.part.forward(x, target, ctx)
         if branch and hasattr(sb.norm_after, "add_into"):
-            sb.norm_after.add_into(target, residual, ctx)          # one kernel, the sum in float32
+            # one kernel, the sum in float32; in bfloat16 it also leaves the new stream in the compute dtype, which the
+            # next branch's projections read if that branch has no norm before it
+            copy = None
+            if ctx is not None and ctx.dtype == torch.bfloat16 and getattr(sb.norm_after, "copies_stream", False):
+                copy = torch.empty(residual.shape, dtype=torch.bfloat16, device=residual.device)
+            if copy is not None:
+                sb.norm_after.add_into(target, residual, ctx, copy=copy)
+                ctx.memo[_STREAM_COPY] = (residual, copy)
+            else:
+                sb.norm_after.add_into(target, residual, ctx)
         elif branch:
             ops.cast_add(sb.norm_after.forward(target, ctx), residual, accumulate=True)
         elif sb.norm_after is not None:

@@ -53,6 +53,7 @@ class LayerNorm(Norm):
     stays float32 (:meth:`add_into`)."""
 
     graph_safe = True
+    copies_stream = True          # add_into can leave the updated stream in bfloat16 as well
 
     def __init__(self, prefix: str, hidden_size: int, eps: float, weight_name: str = "weight", bias_name: str = "bias"):
         join = lambda tail: f"{prefix}.{tail}" if prefix and tail else (prefix or tail)
@@ -82,9 +83,10 @@ class LayerNorm(Norm):
         ops.layernorm(residual, self.weight, self.bias, self.eps, out, rows=rows)
         return out
 
-    def add_into(self, branch, residual, ctx=None) -> None:
-        """``residual += LN(branch)``, both float32: the normed branch is never rounded to the compute dtype."""
-        ops.layernorm(branch, self.weight, self.bias, self.eps, residual, accumulate=True)
+    def add_into(self, branch, residual, ctx=None, copy=None) -> None:
+        """``residual += LN(branch)``, both float32: the normed branch is never rounded to the compute dtype.
+        ``copy`` (bfloat16) receives the updated stream as well, for the projections of the next branch."""
+        ops.layernorm(branch, self.weight, self.bias, self.eps, residual, accumulate=True, copy=copy)
 
 
 register_part("norm", "rmsnorm", RMSNorm)

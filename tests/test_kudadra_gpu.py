@@ -51,8 +51,10 @@ def test_layer_norm_kernel(D, wdtype):
     close(out, want[rows.long()], wdtype, "layer norm of rows")
     acc = torch.randn(13, D)
     out = dev(acc)
-    ops.layernorm(dev(x), dev(w), dev(b), 1e-5, out, accumulate=True)
+    copy = torch.empty(13, D, device=DEV, dtype=torch.bfloat16)
+    ops.layernorm(dev(x), dev(w), dev(b), 1e-5, out, accumulate=True, copy=copy)
     close(out, acc.double() + want, "float32", "layer norm added into the stream")
+    assert torch.equal(copy, out.bfloat16())          # the new stream once more, in bfloat16
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
