@@ -62,8 +62,15 @@ KUD_S = {"architecture": "Kudadra", "vocab": 211, "width": 40, "norm": {"eps": 1
     _with_mlp(_attn(2, 2, 16, 8, 100000, 0), 24, 1.0),
     _with_mlp(_latent(5, 16, 8, 40), None, 0),
 ]}
-CONFIGS = {"P": KUD_P, "Q": KUD_Q, "R": KUD_R, "S": KUD_S}
-PAGE_SIZE = {"P": 16, "Q": 16, "R": 16, "S": 8}
+# T: widths that are multiples of nothing (no 16-byte row anywhere: every kernel's scalar path), odd head sizes, a
+# feed-forward of odd width, a vocabulary of a prime.
+KUD_T = {"architecture": "Kudadra", "vocab": 79, "width": 50, "norm": {"eps": 1e-5}, "layers": [
+    _with_mlp(_ret(2, 10, 7, [0.75, 0.9375], 6, base=300.0), 33, 1.0),
+    _with_mlp(_attn(3, 1, 10, 7, 9, 4), 33, 2.0),
+    _with_mlp(_latent(3, 6, 5, 11), 33, 0.5),
+]}
+CONFIGS = {"P": KUD_P, "Q": KUD_Q, "R": KUD_R, "S": KUD_S, "T": KUD_T}
+PAGE_SIZE = {"P": 16, "Q": 16, "R": 16, "S": 8, "T": 16}
 
 
 def config(name):

@@ -379,7 +379,7 @@ def cancelling_rows(toks, w, cfg, noise=0.02, moved=0.3):
 
 
 LENGTHS = {"P": [1, 2, 17, 33, 70, 150, 64, 49], "Q": [3, 40, 131, 330, 129, 520, 64, 257], "R": [1, 5, 40, 90, 33, 64, 17, 200],
-           "S": [2, 9, 24, 50, 8, 100, 16, 31]}
+           "S": [2, 9, 24, 50, 8, 100, 16, 31], "T": [1, 3, 20, 45, 16, 70, 33, 9]}
 
 
 def build_trace(name, seed=11):
