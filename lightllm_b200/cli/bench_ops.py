@@ -144,6 +144,69 @@ def main(argv=None) -> int:
                                                 btp.shape[1], page, Hq, Hkv, hd, 0, 1 / math.sqrt(hd), cut=cut),
             (2 * T * Hq * hd + 2 * T * Hkv * hd) * 2, 2 * 2 * Hq * hd * T * (T + 1) // 2)
 
+    # ---- the parts of the Kudadra layers: norm on a branch, norm + rotation + cache write, gates, retention, latent attention ---
+    branch, stream = rn(T, D), rn(T, D)
+    w_ln, b_ln = torch.ones(D, dtype=torch.bfloat16, device=dev), torch.zeros(D, dtype=torch.bfloat16, device=dev)
+    stream_bf = torch.empty((T, D), dtype=torch.bfloat16, device=dev)
+    run("layernorm_add_into_stream", lambda: ops.layernorm(branch, w_ln, b_ln, 1e-5, stream, accumulate=True, copy=stream_bf),
+        T * D * (4 + 4 + 4 + 2))
+    Ng = (Hq + 2 * Hkv) * hd + Hq * hd
+    fused = rn(T, Ng, dtype=torch.bfloat16)
+    qn, kn = torch.ones(Hq * hd, device=dev), torch.ones(Hkv * hd, device=dev)
+    run("qkv_prepare_norm_rope_cache", lambda: ops.qkv_prepare(fused, 0, Hq * hd, (Hq + Hkv) * hd, Hq, Hkv, hd, hd, positions,
+                                                               positions, q_out, kc, vc, qn, kn, 1e-5, inv_freq, hd, False),
+        2 * T * Nqkv * 2)
+    attn_bf = rn(T, Hq * hd, dtype=torch.bfloat16)
+    run("head_gate_sigmoid", lambda: ops.head_gate(attn_bf, fused[:, Nqkv:], attn_bf, Hq, hd, False, "sigmoid"), 3 * T * Hq * hd * 2)
+    o_f32 = rn(T, Hq * hd)
+    run("head_gate_unit_rms_silu", lambda: ops.head_gate(o_f32, fused[:, Nqkv:], attn_bf, Hq, hd, False, "silu", unit_rms=True, eps=1e-5),
+        T * Hq * hd * (4 + 2 + 2))
+    gu = rn(T, 2 * I, dtype=torch.bfloat16)
+    act_o = torch.empty((T, I), dtype=torch.bfloat16, device=dev)
+    run("glu_act_clamped", lambda: ops.glu_act(gu, act_o, ops.GLU_CLAMPED_SWISH, 1.702, 7.0, 1.0), 3 * T * I * 2)
+    # retention over one prompt of T rows, in pieces as the engine cuts them (about 16 warps an SM), and one token of B requests
+    Nr = 4 * Hq * hd
+    ret_src = rn(T, Nr, dtype=torch.bfloat16, s=0.5)
+    decay = torch.full((Hq,), 0.99, device=dev)
+    dgs = 1 if hd <= 64 else 2 if hd <= 128 else 4 if hd <= 256 else 8
+    wanted = max(1, 148 * 16 // (Hq * -(-hd * dgs // 32)))
+    chunk = max(32, -(-(-(-T // wanted)) // 16) * 16)
+    npieces = -(-T // chunk)
+    i32r = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    pieces = (i32r([0] * npieces), i32r(list(range(npieces))), i32r([0]), npieces, chunk)
+    st1, ro = torch.zeros((1, Hq, hd, hd), device=dev), torch.empty((T, Hq * hd), device=dev)
+    z1, t1 = i32r([0]), i32r([T])
+    run("retention_prompt_in_pieces", lambda: ops.retention(ret_src, 0, Hq * hd, 2 * Hq * hd, z1, t1, z1, z1, 1, Hq, hd, hd, decay,
+                                                            inv_freq, hd, False, hd ** -0.5, st1, ro, pieces=pieces if npieces > 1 else None),
+        T * Hq * hd * (3 * 2 + 4), 5 * T * Hq * hd * hd)
+    stB, roB = torch.zeros((B, Hq, hd, hd), device=dev), torch.empty((B, Hq * hd), device=dev)
+    rB, oB, pB = i32r(list(range(B))), i32r([1] * B), i32r([C] * B)
+    run("retention_one_token", lambda: ops.retention(ret_src[:B], 0, Hq * hd, 2 * Hq * hd, rB, oB, pB, rB, B, Hq, hd, hd, decay, inv_freq,
+                                                     hd, False, hd ** -0.5, stB, roB), 2 * B * Hq * hd * hd * 4)
+    # attention over a shared latent of 128 (one kv head whose rows are keys and values, sinks): a prompt of T rows
+    rank = 128
+    if ops.attention_tcgen05_supports(rank, page):
+        from lightllm_b200.engine.batch import cut_attention_rows
+        from lightllm_b200.parts import linear as L
+        import numpy as np
+        rows_t = [(0, q0, -(-min(q0 + 128, T) // 128)) for q0 in range(0, T, 128)]
+        items, merges, parts = cut_attention_rows(rows_t, None, Hq, L.num_sms(dev))
+        arr = torch.from_numpy(np.asarray([t[1:] for t in items], dtype=np.int32).T.copy()).to(dev)
+        m = torch.from_numpy(np.asarray(merges, dtype=np.int32).reshape(-1, 4).T.copy()).to(dev)
+        cut = (arr[2], arr[3], arr[4], parts, m[0], m[1], m[2], m[3], len(merges)) if merges else (arr[2], arr[3], arr[4], 0, None, None, None, None, 0)
+        lat = rn(slots, 1, rank, dtype=torch.bfloat16)
+        ql = rn(T, Hq * rank, dtype=torch.bfloat16)
+        ol = torch.empty_like(ql)
+        sinks = torch.zeros(Hq, device=dev)
+        btl = torch.arange(slots // page, dtype=torch.int32, device=dev).reshape(1, -1)
+        run("latent_attention_tcgen05_sinks",
+            lambda: ops.paged_attention_tcgen05(ql, lat, lat, ol, arr[0].contiguous(), arr[1].contiguous(), len(items), z1, t1, z1, btl,
+                                                btl.shape[1], page, Hq, 1, rank, 0, rank ** -0.5, cut=cut, sinks=sinks),
+            (2 * T * Hq * rank + T * rank) * 2, 2 * 2 * Hq * rank * T * (T + 1) // 2)
+        wq_up = rn(Hq, rank, hd, dtype=torch.bfloat16, s=hd ** -0.5)
+        run("head_linear_unfolded_up_projection", lambda: ops.head_linear(fused, 0, wq_up, ql), T * Hq * (hd + rank) * 2,
+            2 * T * Hq * hd * rank)
+
     # ---- what a decode step of B requests over C keys runs --------------------------------------------------------------
     pages_per = -(-(C + 1) // page)
     kcd = rn(B * pages_per * page, Hkv, hd, dtype=torch.bfloat16)

@@ -249,7 +249,7 @@ def test_attention_kernel_with_sinks_and_value_widths(dtype, shape):
 
 
 @pytest.mark.parametrize("hd", [64, 128])
-@pytest.mark.parametrize("window", [0, 200])
+@pytest.mark.parametrize("window", [0, 200, 5, 129])
 def test_tensor_core_attention_with_sinks_over_values_in_the_key_rows(hd, window):
     """The tcgen05 prefill kernel (whole key ranges and ranges cut into pieces that a second kernel merges) and the
     mma.sync decode kernel (pieces merged in a cluster, and through scratch): one kv head whose rows are keys and
