@@ -168,9 +168,10 @@ class LatentAttentionMixer(AttentionMixer):
             wo = self.w_o.double().view(D, H, self.out_dim)
             self.w_o = torch.einsum("khe,her->khr", wo, uv.double()).reshape(D, H * r).to(self.w_o.dtype).contiguous()
         else:
-            # [H, rank, dim]: row o of head h is column o of that head's key up-projection
-            self.w_q_up = uk.to(wdt).transpose(1, 2).contiguous()
-            self.w_v_up = uv.to(wdt).contiguous()
+            # [H, rank, dim]: row o of head h is column o of that head's key up-projection.  The per-head contraction
+            # takes its weights in the activations' dtype (also where a checkpoint stores them in 32 bits)
+            self.w_q_up = uk.to(dtype).transpose(1, 2).contiguous()
+            self.w_v_up = uv.to(dtype).contiguous()
         self.w_fused = torch.cat([w.to(wdt) for w in ws], dim=0).contiguous()
         self.c_norm_w = tensors[self._n("dkv", "norm")].float().contiguous()
         if self.has_sinks:

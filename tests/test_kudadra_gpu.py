@@ -603,3 +603,64 @@ def test_gated_activation_in_the_contractions_epilogue(dtype, M):
             L.FUSE_GLU = True
         close(fused, want, dtype, f"fused clamped gate {M}x{K_}x{I}", rel=None if dtype == "float32" else 1e-2)
         close(apart, want, dtype, f"clamped gate behind the contraction {M}x{K_}x{I}", rel=None if dtype == "float32" else 1.5e-2)
+
+
+def test_command_lines_serve_the_design(tmp_path):
+    """``random_model`` writes a folder from a config.json of the design; ``generate`` continues a prompt greedily as the
+    plain implementation does and samples the same tokens for the same seed; ``bench_server`` runs its users."""
+    import json
+    import re
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+    def run_cli(module, *args):
+        env = dict(os.environ, PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""))
+        proc = subprocess.run([sys.executable, "-m", module, *map(str, args)], stdout=subprocess.PIPE, stderr=subprocess.PIPE,
+                              text=True, env=env, timeout=600, cwd=root)
+        assert proc.returncode == 0, proc.stderr[-3000:]
+        return proc.stdout
+
+    cfg = config("P")
+    cfg_path = str(tmp_path / "config.json")
+    with open(cfg_path, "w") as f:
+        json.dump(cfg, f)
+    d = str(tmp_path / "model")
+    run_cli("lightllm_b200.cli.random_model", cfg_path, d, 4, "--store-dtype", "float32")
+    from tests.plain.qwen2_plain import read_safetensors
+    w = {k: v.double() for k, v in read_safetensors(os.path.join(d, "model.safetensors")).items()}
+    prompt = [5, 17, 3, 99, 250, 7]
+    out = run_cli("lightllm_b200.cli.generate", d, *prompt, "--temperature", 0, "--max-new-tokens", 8, "--dtype", "float32",
+                  "--max-seq-len", 64)
+    got = [int(t) for t in re.search(r"generated:\s*([\d ]+)", out).group(1).split()]
+    seq = list(prompt)
+    for tok in got:
+        lg = K.plain_forward(seq, w, cfg)[-1]
+        top = torch.topk(lg, 2).values
+        assert tok == int(torch.argmax(lg)) or float(top[0] - top[1]) < 1e-4, (seq, tok)
+        seq.append(tok)
+    assert len(got) == 8
+    pick = lambda s: re.search(r"generated:\s*([\d ]+)", s).group(1)
+    a = run_cli("lightllm_b200.cli.generate", d, 1, 2, 3, "--seed", 5, "--max-seq-len", 64)
+    b = run_cli("lightllm_b200.cli.generate", d, 1, 2, 3, "--seed", 5, "--max-seq-len", 64)
+    assert pick(a) == pick(b)
+    out = run_cli("lightllm_b200.cli.bench_server", d, 128, 64)
+    assert "Hidden dim=44" in out and "vocab=301" in out
+
+
+@pytest.mark.parametrize("name", ["P", "Q"])
+def test_weights_stored_in_32_bits_served_in_bfloat16(tmp_path, name):
+    """A folder stored in float32 run with bfloat16 activations: tensors stored in 32 bits stay so (CUDA-core
+    contractions with bfloat16 operands and float weights), the attention and recurrence kernels are the bfloat16 ones."""
+    cfg = config(name)
+    w = random_weights(cfg, 12, store=torch.float32)
+    d = write_model(cfg, w, str(tmp_path / "model32"))
+    wd = {k: v.double() for k, v in w.items()}
+    rng = random.Random(5)
+    toks = [rng.randrange(cfg["vocab"]) for _ in range(150)]
+    plain = K.plain_forward(toks, wd, cfg).float()
+    got = stepwise(core_for(d, "bfloat16", name), "a", toks, [70, 2, 33, 30])
+    tol = atol_for(name, "bfloat16", plain)
+    keep = well_conditioned(toks, wd, cfg, plain, tol)
+    record(f"Kudadra {name} float32-stored bfloat16", error(got, plain, "bfloat16", keep), logits_std(plain))
+    assert error(got, plain, "bfloat16", keep) <= tol and keep.float().mean() > 0.95
