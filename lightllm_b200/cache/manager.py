@@ -234,9 +234,13 @@ class CacheManager:
                 raise CacheError(f"request {seq_id!r} advanced to {new_len} tokens without pages for them")
         seq.length = new_len
         for g, spec in enumerate(self.layout.groups):
-            if spec.window is None:
+            if spec.window is None and not spec.chunk:
                 continue
-            first_needed_pos = new_len - spec.window + 1       # the next query sees keys from here
+            first_needed_pos = 0
+            if spec.window is not None:
+                first_needed_pos = new_len - spec.window + 1       # the next query sees keys from here
+            if spec.chunk:                                         # ... and none before its own block of positions
+                first_needed_pos = max(first_needed_pos, new_len - new_len % spec.chunk)
             dead = max(0, first_needed_pos) // self.page_size   # logical pages wholly before it
             table = seq.tables[g]
             for lp in range(seq.first_live[g], min(dead, len(table))):

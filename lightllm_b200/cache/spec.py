@@ -16,12 +16,14 @@ class KVSpec:
     """Keys and values per token: ``kv_heads * head_dim`` keys and ``kv_heads * v_head_dim`` values.
     ``window`` = how many of the latest positions (the token itself included) stay visible; ``None`` = all of
     them.  ``v_head_dim``: ``None`` = as wide as the keys; 0 = no values are kept (a mixer that reads its values
-    out of the key rows, e.g. attention over a shared latent)."""
+    out of the key rows, e.g. attention over a shared latent).  ``chunk``: a query only sees the positions of its own
+    block of ``chunk`` positions (blocks counted from position 0), so the pages of earlier blocks are given back."""
 
     kv_heads: int
     head_dim: int
     window: Optional[int] = None
     v_head_dim: Optional[int] = None
+    chunk: Optional[int] = None
 
     @property
     def value_dim(self) -> int:

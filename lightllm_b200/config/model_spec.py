@@ -103,10 +103,13 @@ class RunEntry:
 
     ``cache_of`` is ``None`` when this run owns a cache plane (it writes its own keys
     and values or state), or the index of an earlier run entry whose plane it reads
-    without writing."""
+    without writing.  ``enter`` is a part of role ``stream`` that rewrites the residual stream
+    right before this run of the layer (e.g. the re-injection of the embedding at the start of
+    each pass of a looped stretch of layers); it owns no cache."""
 
     layer: int
     cache_of: Optional[int] = None
+    enter: Optional[PartSpec] = None
 
 
 @dataclass

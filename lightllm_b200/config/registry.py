@@ -20,23 +20,30 @@ class Architecture:
     name: str
     config_from_dict: Callable[[Dict[str, Any], str], ModelConfig]
     build_spec: Callable[[ModelConfig], ModelSpec]
+    # True: sizes that config.json does not give are read from the checkpoint's tensor shapes; config_from_dict then
+    # takes ``tensor_shapes={name: shape}`` as a third argument when a model folder is loaded.
+    reads_shapes: bool = False
 
 
 _ARCHITECTURES: Dict[str, Architecture] = {}
 _PARTS: Dict[str, Dict[str, Type]] = {
-    "mixer": {}, "ffn": {}, "norm": {}, "position": {}, "embedding": {}, "head": {}}
+    "mixer": {}, "ffn": {}, "norm": {}, "position": {}, "embedding": {}, "head": {}, "stream": {}}
 
 
-def register_architecture(name: str, config_from_dict, build_spec, replace: bool = False) -> None:
-    """Make ``name`` (as written in ``architectures[0]``) loadable."""
+def register_architecture(name: str, config_from_dict, build_spec, replace: bool = False,
+                          reads_shapes: bool = False) -> None:
+    """Make ``name`` (as written in ``architectures[0]``) loadable.  ``reads_shapes``: the configuration takes the
+    sizes that its config.json leaves out from the shapes of the checkpoint's tensors
+    (``config_from_dict(raw, where, tensor_shapes=...)``)."""
     if name in _ARCHITECTURES and not replace:
         raise ValueError(f"architecture {name!r} is already registered")
-    _ARCHITECTURES[name] = Architecture(name, config_from_dict, build_spec)
+    _ARCHITECTURES[name] = Architecture(name, config_from_dict, build_spec, reads_shapes)
 
 
 def register_part(role: str, kind: str, cls: Type, replace: bool = False) -> None:
     """Make a part class buildable from ``PartSpec(kind=...)`` in the given role
-    (``mixer``, ``ffn``, ``norm``, ``position``, ``embedding`` or ``head``)."""
+    (``mixer``, ``ffn``, ``norm``, ``position``, ``embedding``, ``head`` or ``stream``: a part that
+    rewrites the residual stream before a run entry)."""
     if role not in _PARTS:
         raise ValueError(f"unknown part role {role!r}; roles are {sorted(_PARTS)}")
     if kind in _PARTS[role] and not replace:
@@ -77,7 +84,19 @@ def config_from_dict(raw: Dict[str, Any], where: str = "config.json") -> ModelCo
 def load_config(model_dir: str) -> ModelConfig:
     """Read ``model_dir/config.json`` into the typed configuration of its architecture."""
     import os
-    return config_from_dict(read_config_json(model_dir), os.path.join(model_dir, "config.json"))
+    raw = read_config_json(model_dir)
+    where = os.path.join(model_dir, "config.json")
+    _ensure_builtin()
+    arch = _ARCHITECTURES.get(architecture_name(raw, where))
+    if arch is not None and arch.reads_shapes:
+        from ..weights.safetensors_io import Checkpoint
+        ckpt = Checkpoint(model_dir)
+        try:
+            shapes = {name: tuple(info.shape) for name, info in ckpt.tensors.items()}
+        finally:
+            ckpt.close()
+        return arch.config_from_dict(raw, where, tensor_shapes=shapes)
+    return config_from_dict(raw, where)
 
 
 def model_spec_for(config: ModelConfig) -> ModelSpec:

@@ -95,7 +95,7 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_decode_mma_kernel(DecodePar
     const int qpos = p.span_pos[span] + q0;
     const int* bt = p.block_table + (size_t)span * p.max_pages;
     const int hi = qpos + 1;
-    const int lo = p.window > 0 ? max(0, qpos - p.window + 1) : 0;
+    const int lo = llb_first_visible(qpos, p.window);
     int klo = lo, khi = hi;
     if (p.nsplit > 1) {
         int chunk = (hi - lo + p.nsplit - 1) / p.nsplit;

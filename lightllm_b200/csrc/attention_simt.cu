@@ -75,8 +75,7 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_kernel(AttnParams
 
     // Key range of the tile: [lo, hi); of this split: [klo, khi).
     const int hi = pos0 + nrows;
-    int lo = 0;
-    if (p.window > 0) lo = max(0, pos0 - p.window + 1);
+    const int lo = llb_first_visible(pos0, p.window);
     int klo = lo, khi = hi;
     if (p.nsplit > 1) {
         int chunk = (hi - lo + p.nsplit - 1) / p.nsplit;
@@ -122,7 +121,7 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_attention_kernel(AttnParams
             const int r = v / G;
             if (r >= nrows) continue;  // uniform over the warp
             const int qpos = pos0 + r;
-            const bool visible = kpos < khi && kpos <= qpos && (p.window <= 0 || qpos - kpos < p.window);
+            const bool visible = kpos < khi && kpos <= qpos && kpos >= llb_first_visible(qpos, p.window);
             float s = -INFINITY;
             if (visible) {
                 const float* qv = Qs + (size_t)v * hd;
@@ -281,7 +280,7 @@ __global__ void __launch_bounds__(NWARPS * 32) paged_decode_kernel(AttnParams p)
     const T* vc = (const T*)p.v_cache;
 
     const int hi = qpos + 1;
-    const int lo = p.window > 0 ? max(0, qpos - p.window + 1) : 0;
+    const int lo = llb_first_visible(qpos, p.window);
     int klo = lo, khi = hi;
     if (p.nsplit > 1) {
         int chunk = (hi - lo + p.nsplit - 1) / p.nsplit;

@@ -133,7 +133,7 @@ __device__ __forceinline__ Item make_item(const AttnTcParams& p, int idx) {
     it.nrows = min(BQ, p.span_len[it.span] - q0);
     it.pos0 = p.span_pos[it.span] + q0;
     it.hi = it.pos0 + it.nrows;                                    // keys [lo, hi) can be visible
-    it.lo = p.window > 0 ? max(0, it.pos0 - p.window + 1) : 0;
+    it.lo = llb_first_visible(it.pos0, p.window);
     const int k_first = p.tile_k0 ? p.tile_k0[tile] : 0;
     it.kt0 = (it.lo / BKV) * BKV + k_first * BKV;
     const int all_tiles = (it.hi - (it.lo / BKV) * BKV + BKV - 1) / BKV - k_first;
@@ -345,7 +345,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             if (it.ntiles <= 0) continue;
             const int qpos = it.pos0 + r;
             // visible keys of this row: positions vis_lo .. vis_hi
-            const int vis_lo = p.window > 0 ? max(it.lo, qpos - p.window + 1) : it.lo;
+            const int vis_lo = max(it.lo, llb_first_visible(qpos, p.window));
             const int vis_hi = min(qpos, it.hi - 1);
             float o[HO];
 #pragma unroll
@@ -373,7 +373,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 // Softmax of this thread's row over its 64 keys of the tile, in two passes over tensor memory
                 // (maximum first, then the probabilities), 32 columns at a time.  Tiles that lie wholly below
                 // the diagonal and inside the window of every row of the block skip the masking.
-                const bool interior = (kt + BKV - 1 <= it.pos0) && (p.window <= 0 || (it.pos0 + BQ - 1) - kt < p.window);
+                const bool interior = (kt + BKV - 1 <= it.pos0) && kt >= llb_first_visible(it.pos0 + BQ - 1, p.window);
                 const int c_lo = vis_lo - kt, c_hi = vis_hi - kt;
                 float m_tile;
                 if (interior) m_tile = row_max<false>(tmem_s, 2 * half, c_lo, c_hi);

@@ -72,3 +72,15 @@ struct LlbGluArgs {
 static inline LlbGluArgs llb_glu_silu() { return LlbGluArgs{LLB_GLU_SILU, 1.0f, 0.0f, 0.0f}; }
 
 static inline int llb_ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// The first key position that a query at position qpos sees, under the one `window` argument of the attention kernels:
+//   window > 0   the latest `window` positions, the query's own included (a sliding window);
+//   window < 0   the positions of the query's own block of -window positions, blocks counted from position 0 of the
+//                sequence (chunked attention: floor(qpos / size) == floor(kpos / size));
+//   window == 0  every earlier position.
+// It never decreases with qpos, so the first row of a tile of consecutive queries has the lowest bound.
+__host__ __device__ __forceinline__ int llb_first_visible(int qpos, int window) {
+    if (window > 0) return qpos - window + 1 > 0 ? qpos - window + 1 : 0;
+    if (window < 0) return qpos - qpos % (-window);
+    return 0;
+}

@@ -18,7 +18,8 @@ __global__ void glu_act_kernel(const T* __restrict__ in, T* __restrict__ out, lo
 template <typename TX, typename TG, typename TO>
 __global__ void __launch_bounds__(256) head_gate_kernel(const TX* __restrict__ x, const TG* __restrict__ gate,
                                                         long long gate_stride, TO* __restrict__ out, int T, int H, int hd,
-                                                        int unit_rms, float eps, int per_head, int act) {
+                                                        int unit_rms, float eps, int per_head, int act,
+                                                        const float* __restrict__ norm_w) {
     const int lane = threadIdx.x & 31;
     const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (item >= (long long)T * H) return;
@@ -38,16 +39,18 @@ __global__ void __launch_bounds__(256) head_gate_kernel(const TX* __restrict__ x
     for (int d = lane; d < hd; d += 32) {
         const float z = llb_to_float(gr[per_head ? 0 : d]);
         const float a = act == 0 ? 1.0f / (1.0f + expf(-z)) : llb_silu(z);
-        o[d] = llb_from_float<TO>(llb_to_float(xr[d]) * inv * a);
+        float y = llb_to_float(xr[d]) * inv;
+        if (norm_w) y *= norm_w[d];
+        o[d] = llb_from_float<TO>(y * a);
     }
 }
 
 template <typename TX, typename TG, typename TO>
 int launch_head_gate(const void* x, const void* gate, long long gate_stride, void* out, int T, int H, int hd,
-                     int unit_rms, float eps, int per_head, int act, cudaStream_t s) {
+                     int unit_rms, float eps, int per_head, int act, const float* norm_w, cudaStream_t s) {
     const long long items = (long long)T * H;
     head_gate_kernel<TX, TG, TO><<<(unsigned)((items + 7) / 8), 256, 0, s>>>(
-        (const TX*)x, (const TG*)gate, gate_stride, (TO*)out, T, H, hd, unit_rms, eps, per_head, act);
+        (const TX*)x, (const TG*)gate, gate_stride, (TO*)out, T, H, hd, unit_rms, eps, per_head, act, norm_w);
     return llb_check_launch("head_gate");
 }
 
@@ -72,17 +75,19 @@ LLB_EXPORT int llb_glu_act(const void* in, void* out, int dtype, int M, int I, i
 
 // x [T, H, hd] (float or the activation dtype); gate: row t starts at gate + t * gate_stride and holds H values
 // (per_head) or H*hd; out [T, H, hd] in the activation dtype.  out = (unit_rms ? x / sqrt(mean_head(x^2) + eps) : x)
-// * act(gate), act 0 = sigmoid, 1 = SiLU.  x_dtype: dtype of x; dtype: of gate and out.
+// * act(gate), act 0 = sigmoid, 1 = SiLU.  x_dtype: dtype of x; dtype: of gate and out.  norm_w: float [hd] or null, a weight
+// on the (normed) head shared by all heads, applied before the gate.
 LLB_EXPORT int llb_head_gate(const void* x, int x_dtype, const void* gate, long long gate_stride, void* out, int dtype,
-                             int T, int H, int hd, int unit_rms, float eps, int per_head, int act, cudaStream_t stream) {
+                             int T, int H, int hd, int unit_rms, float eps, int per_head, int act, const float* norm_w,
+                             cudaStream_t stream) {
     if (T == 0) return 0;
     LLB_REQUIRE(T > 0 && H > 0 && hd > 0 && x && gate && out, "head_gate: bad arguments");
     LLB_REQUIRE(act == 0 || act == 1, "head_gate: unknown activation %d", act);
     if (x_dtype == LLB_F32 && dtype == LLB_F32)
-        return launch_head_gate<float, float, float>(x, gate, gate_stride, out, T, H, hd, unit_rms, eps, per_head, act, stream);
+        return launch_head_gate<float, float, float>(x, gate, gate_stride, out, T, H, hd, unit_rms, eps, per_head, act, norm_w, stream);
     if (x_dtype == LLB_F32 && dtype == LLB_BF16)
-        return launch_head_gate<float, __nv_bfloat16, __nv_bfloat16>(x, gate, gate_stride, out, T, H, hd, unit_rms, eps, per_head, act, stream);
+        return launch_head_gate<float, __nv_bfloat16, __nv_bfloat16>(x, gate, gate_stride, out, T, H, hd, unit_rms, eps, per_head, act, norm_w, stream);
     if (x_dtype == LLB_BF16 && dtype == LLB_BF16)
-        return launch_head_gate<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(x, gate, gate_stride, out, T, H, hd, unit_rms, eps, per_head, act, stream);
+        return launch_head_gate<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(x, gate, gate_stride, out, T, H, hd, unit_rms, eps, per_head, act, norm_w, stream);
     return llb_fail("head_gate: unsupported dtypes %d, %d", x_dtype, dtype);
 }

@@ -1,4 +1,4 @@
-// Layer normalisation with weight and bias over rows of a float stream, optionally only over a list of rows, and
+// Layer normalisation with weight and (optionally) bias over rows of a float stream, optionally only over a list of rows, and
 // optionally added into a float destination (a norm on a branch's output: h += LN(branch) in one pass).
 //
 //     mean = sum_d x_d / D;  var = sum_d (x_d - mean)^2 / D;  y_d = (x_d - mean) / sqrt(var + eps) * w_d + b_d
@@ -67,7 +67,7 @@ __global__ void __launch_bounds__(256) layernorm_kernel(const float* __restrict_
         for (int i = 0; i < PER_THREAD; ++i) {
             const int d = threadIdx.x + i * blockDim.x;
             if (d < D) {
-                float y = (v[i] - mean) * inv * llb_to_float(w[d]) + llb_to_float(b[d]);
+                float y = (v[i] - mean) * inv * llb_to_float(w[d]) + (b ? llb_to_float(b[d]) : 0.0f);
                 if (ACCUMULATE) y += llb_to_float(o[d]);
                 o[d] = llb_from_float<TO>(y);
                 if (copy) copy[(size_t)r * D + d] = __float2bfloat16_rn(y);
@@ -75,7 +75,7 @@ __global__ void __launch_bounds__(256) layernorm_kernel(const float* __restrict_
         }
     } else {
         for (int d = threadIdx.x; d < D; d += blockDim.x) {
-            float y = (xr[d] - mean) * inv * llb_to_float(w[d]) + llb_to_float(b[d]);
+            float y = (xr[d] - mean) * inv * llb_to_float(w[d]) + (b ? llb_to_float(b[d]) : 0.0f);
             if (ACCUMULATE) y += llb_to_float(o[d]);
             o[d] = llb_from_float<TO>(y);
             if (copy) copy[(size_t)r * D + d] = __float2bfloat16_rn(y);
@@ -131,7 +131,7 @@ __global__ void __launch_bounds__(256) layernorm_warp_kernel(const float* __rest
     for (int i = 0; i < NV; ++i) {
         const int d = (i * 32 + lane) * 4;
         if (d < D) {
-            const float4 g = ln_load4(w + d), c = ln_load4(b + d);
+            const float4 g = ln_load4(w + d), c = b ? ln_load4(b + d) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
             float4 y = make_float4(v[i].x * inv * g.x + c.x, v[i].y * inv * g.y + c.y, v[i].z * inv * g.z + c.z,
                                    v[i].w * inv * g.w + c.w);
             if (ACCUMULATE) {
@@ -179,13 +179,13 @@ int dispatch_ln(int out_dtype, int accumulate, const float* x, const void* w, co
 
 }  // namespace
 
-// x float [*, D]; w, b [D] (float or bf16, the same for both); out [R, D]; rows: R source rows of x or null for
+// x float [*, D]; w, b [D] (float or bf16, the same for both; b may be null: no bias); out [R, D]; rows: R source rows of x or null for
 // rows 0..R-1; accumulate != 0: out += LN(x) (out must not be x); copy: bf16 [R, D] or null, receives what was
 // written to out (the updated stream, for the next branch's projections).
 LLB_EXPORT int llb_layernorm(const float* x, const void* w, const void* b, int w_dtype, void* out, int out_dtype,
                              const int* rows, int R, int D, float eps, int accumulate, void* copy, cudaStream_t stream) {
     if (R == 0) return 0;
-    LLB_REQUIRE(R > 0 && D > 0 && x && w && b && out, "layernorm: bad arguments R=%d D=%d", R, D);
+    LLB_REQUIRE(R > 0 && D > 0 && x && w && out, "layernorm: bad arguments R=%d D=%d", R, D);
     __nv_bfloat16* c = (__nv_bfloat16*)copy;
     if (w_dtype == LLB_F32) return dispatch_ln<float>(out_dtype, accumulate, x, w, b, out, rows, R, D, eps, c, stream);
     if (w_dtype == LLB_BF16) return dispatch_ln<__nv_bfloat16>(out_dtype, accumulate, x, w, b, out, rows, R, D, eps, c, stream);

@@ -17,7 +17,7 @@ from . import build as _build
 
 F32, BF16 = 0, 1
 EPI_STORE, EPI_STORE_F32, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2, 3
-ABI_VERSION = 22
+ABI_VERSION = 23
 
 _lib: Optional[ctypes.CDLL] = None
 
@@ -137,13 +137,21 @@ def current_stream() -> int:
     return _stream()
 
 
-def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, err: Optional[torch.Tensor] = None) -> None:
-    """out[t,:] = table[ids[t],:] as float.  ids int32 [T], table [V,D], out float32 [T,D]."""
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor, err: Optional[torch.Tensor] = None,
+              scale: float = 1.0, copy: Optional[torch.Tensor] = None) -> None:
+    """out[t,:] = table[ids[t],:] * scale as float.  ids int32 [T], table [V,D], out float32 [T,D]; ``copy`` ([T,D] in
+    the table's dtype) receives the same rows."""
     T, (V, D) = ids.numel(), table.shape
     if out.dtype != torch.float32 or tuple(out.shape) != (T, D):
         raise KernelError(f"embedding: out must be float32 [{T},{D}], got {out.dtype} {tuple(out.shape)}")
-    _check(lib().llb_embedding(_i32(ids, "ids"), _ptr(table), _dt(table), _ptr(out), T, D, V,
-                               _i32(err, "err"), _stream()))
+    if scale == 1.0 and copy is None:
+        _check(lib().llb_embedding(_i32(ids, "ids"), _ptr(table), _dt(table), _ptr(out), T, D, V,
+                                   _i32(err, "err"), _stream()))
+        return
+    if copy is not None and (copy.dtype != table.dtype or tuple(copy.shape) != (T, D)):
+        raise KernelError(f"embedding: copy must be {table.dtype} [{T},{D}]")
+    _check(lib().llb_embedding_scaled(_i32(ids, "ids"), _ptr(table), _dt(table), _ptr(out), T, D, V, _i32(err, "err"),
+                                      ctypes.c_float(scale), _ptr(copy), _stream()))
 
 
 def cast_add(src: torch.Tensor, dst: torch.Tensor, accumulate: bool = False) -> None:
@@ -266,16 +274,16 @@ def _f32(t: Optional[torch.Tensor], what: str) -> Optional[int]:
     return _ptr(t)
 
 
-def layernorm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float, out: torch.Tensor,
+def layernorm(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], eps: float, out: torch.Tensor,
               rows: Optional[torch.Tensor] = None, accumulate: bool = False, copy: Optional[torch.Tensor] = None) -> None:
     """out[r,:] = LN(x[rows[r],:]) * weight + bias (rows = None: row r), or out += ... with ``accumulate``.
-    x float32; weight and bias share a dtype; out float32 or bfloat16.  ``copy`` (bfloat16, out's shape) receives what
+    x float32; weight and bias share a dtype (``bias`` None: none is added); out float32 or bfloat16.  ``copy`` (bfloat16, out's shape) receives what
     was written to out as well."""
     if copy is not None and (copy.dtype != torch.bfloat16 or copy.numel() != out.numel()):
         raise KernelError("layernorm: copy must be bfloat16 of out's size")
     D = x.shape[-1]
     R = rows.numel() if rows is not None else x.numel() // D
-    if x.dtype != torch.float32 or weight.numel() != D or bias.numel() != D or weight.dtype != bias.dtype \
+    if x.dtype != torch.float32 or weight.numel() != D or (bias is not None and (bias.numel() != D or weight.dtype != bias.dtype)) \
             or out.numel() != R * D:
         raise KernelError(f"layernorm: x {x.dtype} {tuple(x.shape)}, weight {tuple(weight.shape)}, out {tuple(out.shape)}")
     _check(lib().llb_layernorm(_ptr(x), _ptr(weight), _ptr(bias), _dt(weight), _ptr(out), _dt(out), _i32(rows, "rows"),
@@ -297,8 +305,10 @@ def glu_act(x: torch.Tensor, out: torch.Tensor, kind: int, alpha: float = 1.0, l
 
 
 def head_gate(x: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, num_heads: int, head_dim: int,
-              per_head: bool, act: str, unit_rms: bool = False, eps: float = 0.0) -> None:
-    """out[t,h,:] = (x[t,h,:], or x / rms(x) over the head with ``unit_rms``) * act(gate), act ``sigmoid`` or ``silu``.
+              per_head: bool, act: str, unit_rms: bool = False, eps: float = 0.0,
+              norm_weight: Optional[torch.Tensor] = None) -> None:
+    """out[t,h,:] = (x[t,h,:], or x / rms(x) over the head with ``unit_rms``) * act(gate), act ``sigmoid`` or ``silu``;
+    ``norm_weight`` (float32 [head_dim], shared by the heads) multiplies the normed head before the gate.
     ``gate`` is a [T, H] (``per_head``) or [T, H*head_dim] view whose rows may be strided (columns of a wider tensor).
     x float32 or the dtype of gate and out."""
     T = x.shape[0]
@@ -307,11 +317,14 @@ def head_gate(x: torch.Tensor, gate: torch.Tensor, out: torch.Tensor, num_heads:
         raise KernelError(f"head_gate: gate must be {out.dtype} [{T},{width}] with unit inner stride")
     if x.numel() != T * num_heads * head_dim or out.numel() != x.numel():
         raise KernelError("head_gate: sizes do not fit")
+    if norm_weight is not None and norm_weight.numel() != head_dim:
+        raise KernelError("head_gate: norm_weight must have one weight per dimension of a head")
     if not gate.is_cuda:
         raise KernelError("tensor is not on a CUDA device; there is no CPU path")
     _check(lib().llb_head_gate(_ptr(x), _dt(x), ctypes.c_void_p(gate.data_ptr()), ctypes.c_longlong(gate.stride(0)),
                                _ptr(out), _dt(out), T, num_heads, head_dim, 1 if unit_rms else 0, ctypes.c_float(eps),
-                               1 if per_head else 0, {"sigmoid": 0, "silu": 1}[act], _stream()))
+                               1 if per_head else 0, {"sigmoid": 0, "silu": 1}[act], _f32(norm_weight, "norm_weight"),
+                               _stream()))
 
 
 def qkv_prepare(src: torch.Tensor, q_off: int, k_off: int, v_off: int, num_heads: int, num_kv_heads: int,
@@ -389,6 +402,146 @@ def retention(src: torch.Tensor, q_off: int, k_off: int, v_off: int, span_row: t
                                v_head_dim, _f32(decay, "decay"), _f32(inv_freq, "inv_freq"), rotary_dim,
                                1 if interleaved else 0, ctypes.c_float(k_scale), _ptr(state), _ptr(scratch), _ptr(out),
                                _stream()))
+
+
+# ---- short convolution, delta rule, routing (csrc/short_conv.cu, csrc/delta_rule.cu, csrc/moe.cu) -------------------------
+CONV_NORMS = {None: 0, "rms": 1, "unit": 2}
+
+
+class ConvSegment:
+    """One of the up to three head groups (q, k, v) that :func:`conv_prepare` makes from the convolved channels:
+    ``col0`` first channel, ``heads`` x ``head_dim``, ``act`` None or ``"silu"``, ``rotary_dim`` leading dimensions
+    rotated, ``norm`` None, ``"rms"`` (unit root mean square) or ``"unit"`` (unit length) with ``eps``, ``scale`` on
+    the result, ``out`` a dense [T, heads*head_dim] tensor or (``to_cache``) the cache rows [slots, heads, head_dim]."""
+
+    def __init__(self, col0: int, heads: int, head_dim: int, out: torch.Tensor, to_cache: bool = False, act=None,
+                 rotary_dim: int = 0, norm=None, eps: float = 0.0, scale: float = 1.0):
+        self.col0, self.heads, self.head_dim, self.out, self.to_cache = col0, heads, head_dim, out, to_cache
+        self.act, self.rotary_dim, self.norm, self.eps, self.scale = act, rotary_dim, norm, eps, scale
+
+
+def _state_base(state: torch.Tensor):
+    if state.dtype != torch.float32 or not state.is_contiguous() or not state.is_cuda:
+        raise KernelError("the state plane must be contiguous float32 on the device")
+    return state.data_ptr(), state.numel() // state.shape[0]
+
+
+def conv_prepare(src: torch.Tensor, c0: int, channels: int, weight: torch.Tensor, segments, ctx_spans, state,
+                 tail_off: int, slot_mapping: Optional[torch.Tensor] = None, freq: Optional[torch.Tensor] = None,
+                 rot_scale: float = 1.0) -> None:
+    """Short causal convolution (``weight`` float32 [channels, taps]) over columns ``c0 .. c0+channels`` of ``src`` [T, C],
+    then per segment activation, rotation of pairs (2i, 2i+1) by ``positions * freq[i]`` (cos and sin times
+    ``rot_scale``), head norm and scale.  ``ctx_spans = (span_row, span_len, span_pos, span_slot, num_spans)``;
+    ``state`` float32 [slots, ...] holds each request's last ``taps - 1`` inputs at ``tail_off`` floats into its slot
+    (``None`` when ``taps == 1``)."""
+    T, C = src.shape
+    taps = weight.shape[1]
+    if weight.dtype != torch.float32 or weight.shape[0] != channels or c0 + channels > C:
+        raise KernelError(f"conv_prepare: weight {weight.dtype} {tuple(weight.shape)} for {channels} channels of {C} columns")
+    span_row, span_len, span_pos, span_slot, num_spans = ctx_spans
+    base, stride = (None, 0) if state is None else _state_base(state)
+    if state is not None and tail_off + (taps - 1) * channels > stride:
+        raise KernelError("conv_prepare: the tail does not fit in a state slot")
+    n = len(segments)
+    I, Fl, P = ctypes.c_int * n, ctypes.c_float * n, ctypes.c_void_p * n
+    for sg in segments:
+        want = (T * sg.heads * sg.head_dim) if not sg.to_cache else None
+        if not sg.out.is_cuda or not sg.out.is_contiguous() or (want is not None and sg.out.numel() != want):
+            raise KernelError("conv_prepare: a segment's output does not fit")
+        if sg.to_cache and tuple(sg.out.shape[1:]) != (sg.heads, sg.head_dim):
+            raise KernelError("conv_prepare: a segment's cache plane does not fit")
+    _check(lib().llb_conv_prepare(
+        _ptr(src), _dt(src), ctypes.c_longlong(C), c0, channels, taps, T, _f32(weight, "weight"),
+        _i32(span_row, "span_row"), _i32(span_len, "span_len"), _i32(span_pos, "span_pos"), _i32(span_slot, "span_slot"),
+        num_spans, base, ctypes.c_longlong(stride), ctypes.c_longlong(tail_off), _i32(slot_mapping, "slot_mapping"),
+        _f32(freq, "freq"), ctypes.c_float(rot_scale), n, I(*[s.col0 for s in segments]), I(*[s.heads for s in segments]),
+        I(*[s.head_dim for s in segments]), I(*[{None: 0, "silu": 1}[s.act] for s in segments]),
+        I(*[s.rotary_dim for s in segments]), I(*[CONV_NORMS[s.norm] for s in segments]),
+        Fl(*[s.eps for s in segments]), Fl(*[s.scale for s in segments]), P(*[s.out.data_ptr() for s in segments]),
+        I(*[_dt(s.out) for s in segments]), I(*[1 if s.to_cache else 0 for s in segments]), _stream()))
+
+
+def conv_tail_update(src: torch.Tensor, c0: int, channels: int, taps: int, ctx_spans, state: torch.Tensor,
+                     tail_off: int) -> None:
+    """After :func:`conv_prepare` (and every other reader of the old tails): each span's request keeps the inputs of its
+    last ``taps - 1`` positions."""
+    if taps <= 1:
+        return
+    span_row, span_len, span_pos, span_slot, num_spans = ctx_spans
+    base, stride = _state_base(state)
+    _check(lib().llb_conv_tail_update(_ptr(src), _dt(src), ctypes.c_longlong(src.shape[1]), c0, channels, taps,
+                                      _i32(span_row, "span_row"), _i32(span_len, "span_len"), _i32(span_pos, "span_pos"),
+                                      _i32(span_slot, "span_slot"), num_spans, base, ctypes.c_longlong(stride),
+                                      ctypes.c_longlong(tail_off), _stream()))
+
+
+def delta_rule(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, beta: torch.Tensor, ctx_spans,
+               num_heads: int, num_qk_heads: int, head_dim: int, v_head_dim: int, state: torch.Tensor, state_off: int,
+               out: torch.Tensor) -> None:
+    """The gated delta rule over every span (csrc/delta_rule.cu).  q, k float32 [T, G*dim]; v float32 [T, H*vdim]; g float32
+    [T, H*dim] decay factors; ``beta`` a [T, H] view (rows may be strided) of values before the sigmoid; the state
+    [H, dim, vdim] of a request lies ``state_off`` floats into its slot of ``state``; out float32 [T, H*vdim]."""
+    T = q.shape[0]
+    H, G, dim, vdim = num_heads, num_qk_heads, head_dim, v_head_dim
+    for t, n, what in ((q, G * dim, "q"), (k, G * dim, "k"), (v, H * vdim, "v"), (g, H * dim, "g"), (out, H * vdim, "out")):
+        if t.dtype != torch.float32 or t.numel() != T * n:
+            raise KernelError(f"delta_rule: {what} must be float32 [{T}, {n}]")
+    if beta.dim() != 2 or tuple(beta.shape) != (T, H) or beta.stride(1) != 1 or not beta.is_cuda:
+        raise KernelError(f"delta_rule: beta must be [{T}, {H}] with unit inner stride")
+    span_row, span_len, span_pos, span_slot, num_spans = ctx_spans
+    base, stride = _state_base(state)
+    if state_off + H * dim * vdim > stride:
+        raise KernelError("delta_rule: the state does not fit in a slot")
+    _check(lib().llb_delta_rule(_ptr(q), _ptr(k), _ptr(v), _ptr(g), ctypes.c_void_p(beta.data_ptr()),
+                                ctypes.c_longlong(beta.stride(0)), _dt(beta), _i32(span_row, "span_row"),
+                                _i32(span_len, "span_len"), _i32(span_pos, "span_pos"), _i32(span_slot, "span_slot"),
+                                num_spans, H, G, dim, vdim, base, ctypes.c_longlong(stride), ctypes.c_longlong(state_off),
+                                _ptr(out), _stream()))
+
+
+LOW_RANK_MODES = {None: 0, "sigmoid": 1, "decay": 2}
+
+
+def low_rank_up(x: torch.Tensor, x_off: int, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                mode=None, rate: Optional[torch.Tensor] = None) -> None:
+    """out[t, n] = f(sum_r x[t, x_off + r] * w[n, r] + bias[n]) with float sums: the second half of a low-rank pair,
+    read from columns of a fused first projection.  ``mode`` None, ``"sigmoid"`` or ``"decay"``:
+    ``exp(-rate[h] * softplus(.))`` with ``rate`` float32 [H] and n = h * (N / H) + ...; out float32 or bfloat16 [T, N]."""
+    T, C = x.shape
+    N, R = w.shape
+    if x_off + R > C or tuple(out.shape) != (T, N):
+        raise KernelError("low_rank_up: sizes do not fit")
+    per = 1
+    if mode == "decay":
+        if rate is None or N % rate.numel():
+            raise KernelError("low_rank_up: the decay mode needs one rate per head")
+        per = N // rate.numel()
+    _check(lib().llb_low_rank_up(_ptr(x), _dt(x), ctypes.c_longlong(C), x_off, T, R, _ptr(w), _dt(w), N, _f32(bias, "bias"),
+                                 LOW_RANK_MODES[mode], _f32(rate, "rate"), per, _ptr(out), _dt(out), _stream()))
+
+
+def moe_route(x: torch.Tensor, w: torch.Tensor, correction: Optional[torch.Tensor], top: int, scale: float,
+              ids: torch.Tensor, weights: torch.Tensor, dense: torch.Tensor, softmax: bool = False,
+              renormalize: bool = False) -> None:
+    """Routing in float (csrc/moe.cu): x [T, D], w float32 [E, D], correction float32 [E] or None (joins the choice, not
+    the weights); ids int32 [T, top], weights float32 [T, top], dense float32 [T, E] (zero where not chosen)."""
+    T, D = x.shape
+    E = w.shape[0]
+    if w.dtype != torch.float32 or w.shape[1] != D or (correction is not None and correction.numel() != E):
+        raise KernelError("moe_route: the router's weights must be float32 [E, D] and the correction [E]")
+    if ids.dtype != torch.int32 or ids.numel() != T * top or weights.numel() != T * top or dense.numel() != T * E:
+        raise KernelError("moe_route: outputs do not fit")
+    _check(lib().llb_moe_route(_ptr(x), _dt(x), _f32(w, "w"), _f32(correction, "correction"), T, D, E, top,
+                               1 if softmax else 0, 1 if renormalize else 0, ctypes.c_float(scale), _i32(ids, "ids"),
+                               _f32(weights, "weights"), _f32(dense, "dense"), _stream()))
+
+
+def moe_scale(act: torch.Tensor, dense: torch.Tensor, num_experts: int, width: int) -> None:
+    """act [T, E*width] *= dense [T, E] expert by expert, in place (exact zeros where an expert was not chosen)."""
+    T = act.shape[0]
+    if act.numel() != T * num_experts * width or dense.numel() != T * num_experts:
+        raise KernelError("moe_scale: sizes do not fit")
+    _check(lib().llb_moe_scale(_ptr(act), _dt(act), _f32(dense, "dense"), T, num_experts, width, _stream()))
 
 
 DEPI_STORE_F32, DEPI_RESIDUAL, DEPI_SWIGLU, DEPI_ROPE_KV = 1, 2, 3, 4

@@ -109,6 +109,16 @@ def cut_attention_rows(rows, chunk_tiles=None, heads=1, slots=1):
 _chosen_chunk: Dict[tuple, int] = {}      # the piece length chosen for (the rows' key tiles, heads, slots)
 
 
+def first_visible(qpos: int, window: int) -> int:
+    """The first position a query at ``qpos`` sees under the attention kernels' signed mask argument: the latest
+    ``window`` positions (> 0), the query's own block of ``-window`` positions (< 0), or everything (0)."""
+    if window > 0:
+        return max(0, qpos - window + 1)
+    if window < 0:
+        return qpos - qpos % (-window)
+    return 0
+
+
 def rows_as_spans(spans: List[Span], bucket: int, max_rows: int):
     """A mixed step described row by row: every token a span of its own (its request's slot, its own position, its own
     row), then the last row repeated until the rows are a multiple of ``bucket`` (at most ``max_rows``).  Returns the
@@ -237,7 +247,7 @@ class StepContext:
             for q0 in range(0, s.length, 128):
                 pos0 = s.start + q0
                 hi = pos0 + 128 if q0 + 128 <= s.length else s.start + s.length
-                lo = pos0 - window + 1 if window > 0 and pos0 >= window else 0
+                lo = first_visible(pos0, window)
                 rows.append((i, q0, -(-(hi - (lo // 128) * 128) // 128)))
         items, merges, parts = cut_attention_rows(rows, chunk_tiles, heads, slots)
         if not items:

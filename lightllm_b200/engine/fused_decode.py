@@ -44,7 +44,8 @@ def _layer_facts(block, view):
     if a.role != "mixer" or f.role != "ffn" or a.norm_after is not None or f.norm_after is not None:
         return None
     mixer, ffn, n1, n2 = a.part, f.part, a.norm_before, f.norm_before
-    if type(mixer) is not AttentionMixer or type(ffn) is not GatedMLP or type(n1) is not RMSNorm or type(n2) is not RMSNorm:
+    if type(mixer) is not AttentionMixer or type(ffn) is not GatedMLP or type(n1) is not RMSNorm or type(n2) is not RMSNorm \
+            or mixer.chunk:          # (the persistent kernel's attention stage knows windows only)
         return None
     pos = mixer.position
     if type(pos) is RotaryEmbedding:
@@ -117,7 +118,8 @@ class FusedDecode:
                 i += 1
                 continue
             j = i
-            while j < len(facts) and facts[j] is not None and facts[j][0] == facts[i][0]:
+            while j < len(facts) and facts[j] is not None and facts[j][0] == facts[i][0] and \
+                    (j == i or model.run[j].enter is None):          # a run entry that rewrites the stream begins a segment
                 j += 1
             self.segments[i] = Segment(i, j, facts[i][0], [f[1] for f in facts[i:j]], facts[i][2], device)
             i = j

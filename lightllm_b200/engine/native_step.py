@@ -119,7 +119,7 @@ def _layer_record(block, view, dtype):
     rec.norm2 = NormDesc(_addr(n2.weight), code(n2.weight), n2.eps)
     rec.attn = AttentionDesc(_addr(mixer.w_qkv), _addr(mixer.b_qkv), _addr(mixer.w_o), _addr(mixer.b_o), _addr(view.k),
                              _addr(view.v), _addr(inv_freq), view.k.shape[0], 1 if view.writes else 0, view.group,
-                             mixer.num_heads, mixer.num_kv_heads, mixer.head_dim, mixer.window or 0, mixer.scale,
+                             mixer.num_heads, mixer.num_kv_heads, mixer.head_dim, mixer.kernel_window(), mixer.scale,
                              rotary_dim, 1 if interleaved else 0, 0, 0, 0)
     rec.mlp = MlpDesc(_addr(ffn.w_gate_up), _addr(ffn.b_gate_up), _addr(ffn.w_down), _addr(ffn.b_down),
                       ffn.intermediate_size, 0)

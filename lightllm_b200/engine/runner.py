@@ -307,7 +307,10 @@ class ModelRunner:
         residual = m.embedding.forward(ctx.token_ids, ctx)
         fused = self.fused if self.fused.takes(ctx) else None
         i = 0
+        enters = m.enters
         while i < len(m.run):
+            if enters[i] is not None:          # a part that rewrites the stream before this run of the layer
+                enters[i].forward(residual, ctx)
             segment = fused.segment_at(i) if fused is not None else None
             if self._nvtx:
                 torch.cuda.nvtx.range_push(f"run{i}:" + (f"fused to {segment.end}" if segment else f"layer{m.run[i].layer}"))
@@ -316,6 +319,7 @@ class ModelRunner:
                 i = segment.end
             elif self.native.covers[i]:
                 j = self.native.stretch(i)
+                j = next((k for k in range(i + 1, j) if enters[k] is not None), j)
                 if fused is not None:           # up to where the next fused segment begins
                     j = next((k for k in range(i + 1, j) if fused.segment_at(k) is not None), j)
                 self.native.run(residual, ctx, i, j)

@@ -31,6 +31,9 @@ class Model:
         self.final_norm = build_part("norm", spec.final_norm)
         self.head = build_part("head", spec.head)
         self.run = list(spec.run)
+        # parts that rewrite the stream before a run entry (None for most)
+        self.enters: List[Optional[Part]] = [build_part("stream", e.enter) if e.enter is not None else None
+                                             for e in self.run]
         mixers = [self.layers[e.layer].mixer for e in self.run]
         self.cache_layout = CacheLayout.build(
             [m.cache_spec() if m is not None else None for m in mixers], [e.cache_of for e in self.run])
@@ -40,7 +43,7 @@ class Model:
 
     def parts(self) -> List[Part]:
         out: List[Part] = []
-        for top in [self.embedding, *self.layers, self.final_norm, self.head]:
+        for top in [self.embedding, *self.layers, *(e for e in self.enters if e is not None), self.final_norm, self.head]:
             out.extend(_walk(top))
         return out
 
@@ -78,7 +81,7 @@ class Model:
                 for sb in self.layers[entry.layer].subs:
                     for part in sb.parts():
                         add(part, i if part is sb.part and sb.role == "mixer" else None)
-            for part in (self.embedding, self.final_norm, self.head):
+            for part in (self.embedding, *(e for e in self.enters if e is not None), self.final_norm, self.head):
                 add(part, None)
             self._prepare_hooks = hooks
         for hook, run_index in hooks:

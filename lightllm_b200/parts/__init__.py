@@ -2,6 +2,10 @@
 from .base import CacheView, FeedForward, Mixer, Norm, Part, PositionEncoding
 from .attention import AttentionMixer
 from .block import Block, build_part
+from .conv_attention import ConvAttentionMixer
+from .delta import ChannelDeltaMixer
+from .moe import RoutedExperts
+from .stream import StreamReinjection
 from .embedding import LMHead, TokenEmbedding
 from .gated_attention import GatedAttentionMixer, LatentAttentionMixer
 from .mlp import GatedMLP
@@ -11,4 +15,5 @@ from .rotary import NoPositionEncoding, RotaryEmbedding
 
 __all__ = ["CacheView", "FeedForward", "Mixer", "Norm", "Part", "PositionEncoding", "AttentionMixer", "Block",
            "build_part", "LMHead", "TokenEmbedding", "GatedMLP", "RMSNorm", "LayerNorm", "GatedAttentionMixer",
-           "LatentAttentionMixer", "RetentionMixer", "NoPositionEncoding", "RotaryEmbedding"]
+           "LatentAttentionMixer", "RetentionMixer", "NoPositionEncoding", "RotaryEmbedding", "ConvAttentionMixer",
+           "ChannelDeltaMixer", "RoutedExperts", "StreamReinjection"]

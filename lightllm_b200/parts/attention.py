@@ -40,15 +40,20 @@ class AttentionMixer(Mixer):
     (rotation), src/kv_cache/paged_attention.cu:115,153-163 (grouping, scores, softmax),
     engine_server.cpp:1870-1871 (output projection and residual).  Unlike the reference the
     q/k/v biases are loaded and added, a token sees its own key, every portion is causal, and
-    ``window`` limits a query to the latest ``window`` keys (itself included)."""
+    ``window`` limits a query to the latest ``window`` keys (itself included); ``chunk`` to the keys of its own block
+    of ``chunk`` positions, blocks counted from position 0 of the sequence (the kernels take the two as one signed
+    argument: a positive window, or minus the chunk)."""
 
     graph_safe = True
+    takes_rotary_magnitude = False          # whether the mixer's rotation applies the position encoding's `magnitude`
 
     def __init__(self, prefix: str, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position: Optional[PartSpec] = None, qkv_bias: bool = True, out_bias: bool = False,
                  window: Optional[int] = None, scale: Optional[float] = None,
                  names: Optional[Dict[str, str]] = None, weight_suffix: str = ".weight",
-                 v_head_dim: Optional[int] = None):
+                 v_head_dim: Optional[int] = None, chunk: Optional[int] = None):
+        if window and chunk:
+            raise ValueError("an attention mixer takes a window or a chunk, not both")
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} query heads are not a multiple of {num_kv_heads} kv heads")
         self.prefix = prefix
@@ -62,11 +67,15 @@ class AttentionMixer(Mixer):
         self.values_in_keys = False
         self.weight_suffix = weight_suffix
         self.window = window
+        self.chunk = int(chunk) if chunk else None
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
         self.names = {"q": "q_proj", "k": "k_proj", "v": "v_proj", "o": "o_proj"}
         self.names.update(names or {})
         position = position or PartSpec("none")
         self.position = part_class("position", position.kind)(position.prefix, **position.params)
+        if getattr(self.position, "magnitude", 1.0) != 1.0 and not self.takes_rotary_magnitude:
+            raise ValueError(f"{type(self).__name__} rotates with magnitude 1; scaled rotary positions need a mixer "
+                             "whose kernel takes the factor")
         self.w_qkv = self.b_qkv = self.w_o = self.b_o = None
 
     def _n(self, which: str, what: str) -> str:
@@ -79,7 +88,11 @@ class AttentionMixer(Mixer):
 
     def cache_spec(self) -> CacheSpec:
         vd = 0 if self.values_in_keys else (None if self.v_head_dim == self.head_dim else self.v_head_dim)
-        return CacheSpec(kv=KVSpec(self.num_kv_heads, self.head_dim, self.window, vd))
+        return CacheSpec(kv=KVSpec(self.num_kv_heads, self.head_dim, self.window, vd, self.chunk))
+
+    def kernel_window(self) -> int:
+        """The mask as the attention kernels take it: a window > 0, minus the chunk, or 0 for every earlier key."""
+        return -self.chunk if self.chunk else (self.window or 0)
 
     def weight_specs(self) -> List[WeightSpec]:
         D, hq, hkv = self.hidden_size, self.num_heads * self.head_dim, self.num_kv_heads * self.head_dim
@@ -208,7 +221,7 @@ class AttentionMixer(Mixer):
     def _plan(self, ctx, dtype):
         """Which kernels this step's attention takes and over which tiles: made once per step (in
         ``prepare`` when the engine runs it, so that the index arrays travel with the step's metadata)."""
-        window = self.window or 0
+        window = self.kernel_window()
         # the tensor-core kernels take values as wide as the keys (sinks and values in the key rows included)
         plain = self.v_head_dim == self.head_dim
         key = ("attention_plan", self.num_heads, self.num_kv_heads, self.head_dim, window, dtype, plain)
@@ -219,7 +232,7 @@ class AttentionMixer(Mixer):
         if ctx.decode_only:
             S = ctx.num_spans
             bound = ctx.max_pages * ctx.page_size          # the same for every step of this shape
-            span = bound if window == 0 else min(bound, window)
+            span = bound if window == 0 else min(bound, abs(window))
             want = max(1, -(-2 * L.num_sms(ctx.device) // (S * self.num_kv_heads)))       # blocks to fill the SMs twice
             nsplit = max(1, min(want, -(-span // 128)))
             mma = bf16 and ops.paged_decode_mma_supports(self.num_heads, self.num_kv_heads, self.head_dim)
@@ -246,7 +259,7 @@ class AttentionMixer(Mixer):
         tensor, single, rows, rest = [], [], [], []
         rows_keys = 0
         for i, s in enumerate(ctx.spans):
-            keys = s.start + s.length if window == 0 else min(s.start + s.length, window + s.length)
+            keys = s.start + s.length if window == 0 else min(s.start + s.length, abs(window) + s.length)
             if tc_ok and s.length >= TENSOR_CORE_MIN_ROWS:
                 tensor.append(i)
             elif mma_ok and s.length == 1:
@@ -264,7 +277,7 @@ class AttentionMixer(Mixer):
         decode = None
         if single:
             bound = ctx.max_pages * ctx.page_size
-            span = bound if window == 0 else min(bound, window)
+            span = bound if window == 0 else min(bound, abs(window))
             resident = ops.decode_mma_resident(self.head_dim) * L.num_sms(ctx.device) // (len(single) * self.num_kv_heads)
             nsplit = max(1, min(8, ops.decode_mma_cluster_splits(), resident, -(-span // 128)))
             decode = (ctx.tiles(1, select=tuple(single)), nsplit)
@@ -285,7 +298,7 @@ class AttentionMixer(Mixer):
             pos_key = getattr(self.position, "prepare_key", None)
             if pos_key is None:
                 return None
-        return ("attention", self.num_heads, self.num_kv_heads, self.head_dim, self.v_head_dim, self.window or 0,
+        return ("attention", self.num_heads, self.num_kv_heads, self.head_dim, self.v_head_dim, self.kernel_window(),
                 self.sinks is not None, self.values_in_keys, pos_key)
 
     def prepare(self, ctx, cache=None) -> None:
@@ -296,7 +309,7 @@ class AttentionMixer(Mixer):
     def attend(self, q, cache: CacheView, ctx, out) -> None:
         """out[t] = attention of query row t over positions <= its own (within the window)."""
         g = cache.group
-        window = self.window or 0
+        window = self.kernel_window()
         common = (ctx.span_row, ctx.span_len, ctx.span_pos, ctx.block_tables[g], ctx.max_pages, ctx.page_size,
                   self.num_heads, self.num_kv_heads, self.head_dim, window, self.scale)
         plan = self._plan(ctx, q.dtype)

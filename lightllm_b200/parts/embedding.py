@@ -12,17 +12,24 @@ from . import linear as L
 from .base import Part
 
 
+EMBEDDING_OUTPUT = "embedding output in the compute dtype"          # ctx.memo key
+
+
 class TokenEmbedding(Part):
     """``h[t, :] = table[id_t, :]`` into the float32 residual stream (src/ops/embedding.cu:9-18).
-    An id outside the vocabulary is an error, not a clamp to 0 as in the reference."""
+    An id outside the vocabulary is an error, not a clamp to 0 as in the reference.  ``scale`` multiplies the rows;
+    ``keep_output`` leaves a copy of the result in the compute dtype in ``ctx.memo[EMBEDDING_OUTPUT]`` for parts that
+    read the embedding again after layers have changed the stream."""
 
     graph_safe = True
 
     role = "embedding"
 
-    def __init__(self, prefix: str, vocab_size: int, hidden_size: int, weight_name: str = "weight"):
+    def __init__(self, prefix: str, vocab_size: int, hidden_size: int, weight_name: str = "weight", scale: float = 1.0,
+                 keep_output: bool = False):
         self.name = f"{prefix}.{weight_name}" if prefix else weight_name
         self.vocab_size, self.hidden_size = vocab_size, hidden_size
+        self.scale, self.keep_output = float(scale), bool(keep_output)
         self.table = None
 
     def weight_specs(self) -> List[WeightSpec]:
@@ -33,7 +40,16 @@ class TokenEmbedding(Part):
 
     def forward(self, token_ids, ctx=None):
         out = torch.empty((token_ids.numel(), self.hidden_size), dtype=torch.float32, device=token_ids.device)
-        ops.embedding(token_ids, self.table, out, None if ctx is None else ctx.err)
+        copy = None
+        if self.keep_output and ctx is not None:
+            copy = torch.empty(out.shape, dtype=self.table.dtype, device=out.device)
+        ops.embedding(token_ids, self.table, out, None if ctx is None else ctx.err, scale=self.scale, copy=copy)
+        if copy is not None:
+            if copy.dtype != ctx.dtype:          # a table stored in another precision than the activations
+                kept = torch.empty(out.shape, dtype=ctx.dtype, device=out.device)
+                ops.cast_add(out, kept)
+                copy = kept
+            ctx.memo[EMBEDDING_OUTPUT] = copy
         return out
 
 

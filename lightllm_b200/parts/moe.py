@@ -1,0 +1,102 @@
+"""Feed-forward layers made of routed experts."""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from ..config import register_part
+from ..csrc import ops
+from ..weights import WeightSpec
+from . import linear as L
+from .base import FeedForward, LazyNorm
+from .mlp import ACTIVATIONS
+
+
+class RoutedExperts(FeedForward):
+    """``h += sum over the chosen experts e of w_e * W_down_e (act(W_gate_e x) * (W_up_e x))``.
+
+    Routing (float32): logits ``z = W_r x``, scores ``sigmoid(z)`` (or a softmax over the experts with
+    ``score="softmax"``), the ``top`` experts with the largest ``score + correction`` (``correction``: a per-expert
+    tensor that takes part in the choice only, or none), weights = the chosen experts' scores, divided by their sum
+    with ``renormalize``, times ``route_scale``.
+
+    The experts run as two contractions over all of them: gate and up of every expert are the rows of one matrix
+    (interleaved pair by pair, the gated activation in the contraction's epilogue), the activations of expert e are
+    multiplied by w_e (zero for the experts a token did not choose) and the down matrices, side by side along the
+    inner dimension, add the weighted sum into the stream: ``sum_e w_e W_down_e a_e = [W_down_0 .. W_down_E-1]
+    [w_0 a_0; ..; w_E-1 a_E-1]``.  Every launch's shape follows from the step's token count alone, so steps replay
+    from CUDA graphs; the price is that every token meets every expert, ``num_experts / top`` times the arithmetic
+    that a grouped contraction over the chosen pairs would need."""
+
+    graph_safe = True
+    accepts_lazy_norm = False
+
+    def __init__(self, prefix: str, hidden_size: int, intermediate_size: int, num_experts: int, top: int,
+                 route_scale: float = 1.0, score: str = "sigmoid", renormalize: bool = False, correction: bool = False,
+                 activation: str = "silu", names: Optional[Dict[str, str]] = None, weight_suffix: str = ".weight",
+                 expert_prefix: str = "experts."):
+        if not 0 < top <= num_experts:
+            raise ValueError(f"top {top} of {num_experts} experts")
+        if score not in ("sigmoid", "softmax"):
+            raise ValueError(f"score must be 'sigmoid' or 'softmax', got {score!r}")
+        if activation != "silu":
+            raise ValueError(f"routed experts implement the SiLU gate, not {activation!r}")
+        self.prefix, self.hidden_size, self.intermediate_size = prefix, hidden_size, intermediate_size
+        self.num_experts, self.top, self.route_scale = num_experts, top, float(route_scale)
+        self.score, self.renormalize, self.has_correction = score, bool(renormalize), bool(correction)
+        self.activation = ACTIVATIONS[activation]
+        self.names = {"gate": "gate_proj", "up": "up_proj", "down": "down_proj", "router": "router",
+                      "correction": "correction"}
+        self.names.update(names or {})
+        self.weight_suffix, self.expert_prefix = weight_suffix, expert_prefix
+        self.w_router = self.correction = self.w_gate_up = self.w_down = None
+
+    def _e(self, e: int, which: str) -> str:
+        return f"{self.prefix}.{self.expert_prefix}{e}.{self.names[which]}{self.weight_suffix}"
+
+    def weight_specs(self) -> List[WeightSpec]:
+        D, I = self.hidden_size, self.intermediate_size
+        specs = [WeightSpec(f"{self.prefix}.{self.names['router']}{self.weight_suffix}", (self.num_experts, D), init=("normal", 0.1))]
+        if self.has_correction:
+            specs.append(WeightSpec(f"{self.prefix}.{self.names['correction']}", (self.num_experts,), init=("normal", 0.1)))
+        for e in range(self.num_experts):
+            specs += [WeightSpec(self._e(e, "gate"), (I, D)), WeightSpec(self._e(e, "up"), (I, D)),
+                      WeightSpec(self._e(e, "down"), (D, I))]
+        return specs
+
+    def bind(self, tensors, dtype, device) -> None:
+        E, I, D = self.num_experts, self.intermediate_size, self.hidden_size
+        self.w_router = tensors[f"{self.prefix}.{self.names['router']}{self.weight_suffix}"].float().contiguous()
+        if self.has_correction:
+            self.correction = tensors[f"{self.prefix}.{self.names['correction']}"].float().contiguous()
+        gates, ups = [tensors[self._e(e, "gate")] for e in range(E)], [tensors[self._e(e, "up")] for e in range(E)]
+        downs = [tensors[self._e(e, "down")] for e in range(E)]
+        wide = any(w.dtype == torch.float32 for w in gates + ups + downs)
+        wdt = torch.float32 if wide else gates[0].dtype
+        # rows: expert by expert, (gate_j, up_j) adjacent, so that the epilogue writes act(gate) * up in expert order
+        self.w_gate_up = torch.stack([torch.stack([g.to(wdt), u.to(wdt)], dim=1).reshape(2 * I, D)
+                                      for g, u in zip(gates, ups)]).reshape(E * 2 * I, D).contiguous()
+        self.w_down = torch.cat([w.to(wdt) for w in downs], dim=1).contiguous()          # [D, E * I]
+        L.reserve_fused_scratch(device, E * 2 * I)
+
+    def route(self, x):
+        """(ids [T, top] int32, weights [T, top], dense weights [T, E]) of the rows of x."""
+        T = x.shape[0]
+        ids = torch.empty((T, self.top), dtype=torch.int32, device=x.device)
+        weights = torch.empty((T, self.top), dtype=torch.float32, device=x.device)
+        dense = torch.empty((T, self.num_experts), dtype=torch.float32, device=x.device)
+        ops.moe_route(x, self.w_router, self.correction, self.top, self.route_scale, ids, weights, dense,
+                      softmax=self.score == "softmax", renormalize=self.renormalize)
+        return ids, weights, dense
+
+    def forward(self, x, residual, ctx=None) -> None:
+        if isinstance(x, LazyNorm):
+            x = x.materialize()
+        _, _, dense = self.route(x)
+        act = L.linear(x, self.w_gate_up, None, L.SWIGLU)           # [T, E * I]
+        ops.moe_scale(act, dense, self.num_experts, self.intermediate_size)
+        L.linear(act, self.w_down, None, L.RESIDUAL, residual=residual)
+
+
+register_part("ffn", "routed_experts", RoutedExperts)

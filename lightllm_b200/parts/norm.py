@@ -1,7 +1,7 @@
 """RMSNorm of the float32 residual stream."""
 from __future__ import annotations
 
-from typing import Dict, List
+from typing import Dict, List, Optional
 
 import torch
 
@@ -49,27 +49,31 @@ class RMSNorm(Norm):
 class LayerNorm(Norm):
     """``y = (x - mean) / sqrt(var + eps) * weight + bias`` with ``var`` the mean of the squared deviations, all in
     float32.  ``weight_name`` / ``bias_name`` are appended to ``prefix`` with a dot; an empty ``weight_name`` makes the
-    prefix itself the weight's name.  As a norm on a branch's output (``h += LN(branch)``) the sum is one kernel and
+    prefix itself the weight's name; ``bias_name=None`` is a layer norm without a bias.  As a norm on a branch's output (``h += LN(branch)``) the sum is one kernel and
     stays float32 (:meth:`add_into`)."""
 
     graph_safe = True
     copies_stream = True          # add_into can leave the updated stream in bfloat16 as well
 
-    def __init__(self, prefix: str, hidden_size: int, eps: float, weight_name: str = "weight", bias_name: str = "bias"):
+    def __init__(self, prefix: str, hidden_size: int, eps: float, weight_name: str = "weight",
+                 bias_name: Optional[str] = "bias"):
         join = lambda tail: f"{prefix}.{tail}" if prefix and tail else (prefix or tail)
-        self.name, self.bias_name = join(weight_name), join(bias_name)
+        self.name, self.bias_name = join(weight_name), (None if bias_name is None else join(bias_name))
         self.hidden_size = hidden_size
         self.eps = float(eps)
         self.weight = self.bias = None
         self.out_dtype = torch.float32
 
     def weight_specs(self) -> List[WeightSpec]:
-        return [WeightSpec(self.name, (self.hidden_size,), init=("one_plus_normal", 0.1)),
-                WeightSpec(self.bias_name, (self.hidden_size,), init=("normal", 0.1))]
+        specs = [WeightSpec(self.name, (self.hidden_size,), init=("one_plus_normal", 0.1))]
+        if self.bias_name is not None:
+            specs.append(WeightSpec(self.bias_name, (self.hidden_size,), init=("normal", 0.1)))
+        return specs
 
     def bind(self, tensors: Dict[str, torch.Tensor], dtype, device) -> None:
-        self.weight, self.bias = tensors[self.name], tensors[self.bias_name]
-        if self.weight.dtype != self.bias.dtype:
+        self.weight = tensors[self.name]
+        self.bias = tensors[self.bias_name] if self.bias_name is not None else None
+        if self.bias is not None and self.weight.dtype != self.bias.dtype:
             self.weight, self.bias = self.weight.float(), self.bias.float()
         self.out_dtype = dtype
 

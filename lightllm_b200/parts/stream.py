@@ -1,0 +1,58 @@
+"""Parts that rewrite the residual stream between layers (role ``stream``): a run entry may name one as its ``enter``."""
+from __future__ import annotations
+
+from typing import List
+
+import torch
+
+from ..config import register_part
+from ..csrc import ops
+from ..weights import WeightSpec
+from . import linear as L
+from .base import Part
+from .embedding import EMBEDDING_OUTPUT
+
+
+class StreamReinjection(Part):
+    """``h <- W [h; e] + step[index]``: the stream is mixed again with the embedding output ``e`` (kept by the embedding
+    part, ``keep_output=True``) and a learned vector is added, e.g. before every pass of a looped stretch of layers.
+
+    ``weight_name`` is ``[hidden, 2 * hidden]`` with the stream's columns first; ``step_name`` is ``[rows, hidden]`` and
+    ``index`` picks the row.  Parts of several run entries may name the same tensors (one per pass).  The two halves of
+    the contraction run as two contractions that add into the cleared float stream, the step vector as the first one's
+    bias, so the new stream is never rounded to the compute dtype."""
+
+    role = "stream"
+    graph_safe = True
+
+    def __init__(self, prefix: str, hidden_size: int, weight_name: str, step_name: str, steps: int, index: int):
+        if not 0 <= index < steps:
+            raise ValueError(f"step vector {index} of {steps}")
+        join = lambda tail: f"{prefix}.{tail}" if prefix else tail
+        self.weight_name, self.step_name = join(weight_name), join(step_name)
+        self.hidden_size, self.steps, self.index = hidden_size, steps, index
+        self.w_stream = self.w_embedding = self.step = None
+
+    def weight_specs(self) -> List[WeightSpec]:
+        D = self.hidden_size
+        return [WeightSpec(self.weight_name, (D, 2 * D)), WeightSpec(self.step_name, (self.steps, D), init=("normal", 0.1))]
+
+    def bind(self, tensors, dtype, device) -> None:
+        w = tensors[self.weight_name]
+        D = self.hidden_size
+        self.w_stream = w[:, :D].contiguous()
+        self.w_embedding = w[:, D:].contiguous()
+        self.step = tensors[self.step_name][self.index].float().contiguous()
+
+    def forward(self, residual, ctx) -> None:
+        kept = ctx.memo.get(EMBEDDING_OUTPUT)
+        if kept is None:
+            raise ops.KernelError("stream re-injection: the embedding part did not keep its output (keep_output=True)")
+        x = torch.empty(residual.shape, dtype=ctx.dtype, device=residual.device)
+        ops.cast_add(residual, x)
+        residual.zero_()
+        L.linear(x, self.w_stream, self.step, L.RESIDUAL, residual=residual)
+        L.linear(kept, self.w_embedding, None, L.RESIDUAL, residual=residual)
+
+
+register_part("stream", "reinjection", StreamReinjection)
