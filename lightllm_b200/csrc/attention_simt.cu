@@ -534,7 +534,7 @@ LLB_EXPORT long long llb_attention_scratch_floats(int num_tiles, int Hq, int hd,
 // q [T, Hq, hd]; out [T, Hq, hdv]; k_cache [slots, Hkv, hd], v_cache [slots, Hkv, hdv] with slot = page*page_size +
 // offset (v_cache may be k_cache itself with hdv == hd: values read out of the key rows);
 // tile_span, tile_q0 [num_tiles]; span_row, span_len, span_pos [S]; block_table [S, max_pages].
-// window <= 0 means every earlier key is visible.  sinks [Hq] float or null: exp(sinks[h]) is added once to head h's
+// window: > 0 the latest keys, < 0 the query's own block of -window positions, 0 every earlier key (llb_first_visible).  sinks [Hq] float or null: exp(sinks[h]) is added once to head h's
 // softmax denominator (a logit without key or value, not scaled).  scratch: num_tiles*Hq*BQ*nsplit*(hdv+2) floats
 // when nsplit > 1, else unused.
 LLB_EXPORT int llb_paged_attention_ex(const void* q, const void* k_cache, const void* v_cache, void* out, int dtype,

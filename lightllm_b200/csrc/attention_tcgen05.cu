@@ -566,7 +566,7 @@ LLB_EXPORT int llb_attention_tcgen05_supports(int hd, int page_size) {
 
 // q, out [T, Hq, hd] bf16; k_cache, v_cache [num_slots, Hkv, hd] bf16 with slot = page*page_size + offset;
 // tiles of 128 query rows: tile_span, tile_q0 [num_tiles]; span_row, span_len, span_pos [S];
-// block_table [S, max_pages].  window <= 0: every earlier key is visible.  tile_k0 / tile_nk / tile_part (or all
+// block_table [S, max_pages].  window as llb_first_visible takes it (> 0 latest keys, < 0 blocks of positions, 0 all).  tile_k0 / tile_nk / tile_part (or all
 // null) cut tiles into items over ranges of 128-key tiles; items with tile_part >= 0 write partial results to
 // part_scratch (num_parts * Hq * 128 * (hd + 2) floats) for llb_attention_tcgen05_merge.
 // sinks [Hq] float or null: exp(sinks[h]) is added once to head h's softmax denominator (by the kernel for whole
