@@ -5,7 +5,7 @@
     python bench.py --sizes 1.5b|7b          (the larger sizes of the family: a line of their own)
     python bench.py [--sizes ..] --only decode|prefill [--prompt-len N]     (one part, at another context length)
     python bench.py --only small-mixed       (the steps of a loaded server: a 16-token portion beside decoded tokens)
-    python bench.py --design kudadra [--sizes 1.5b] [--layers L]     (the Kudadra design beside Qwen2 at equal sizes)
+    python bench.py --design kudadra|bulitar [--sizes 1.5b] [--layers L]     (another design beside Qwen2 at equal sizes)
 
 Prints one JSON line.  ``value`` is decoded tokens a second over K timed decode steps of a
 batch of 8 requests that each hold a 2,048-token prompt (random weights, random token ids),
@@ -343,17 +343,45 @@ def kudadra_config(base: dict, layers: int, kinds=("latent_attention", "attentio
                         "mlp": {"kind": "dense", "ff": base["intermediate_size"], "limit": 7.0}} for i in range(layers)]}
 
 
+def bulitar_config(base: dict, layers: int, kinds=("attention", "channel_delta"), experts: int = 8, top: int = 2) -> dict:
+    """A Bulitar model with the width, head count, head size and vocabulary of a Qwen2 configuration, run as ``layers``
+    layer runs: the first and the last layer once, the layers between them twice in a row (the loop), so the file holds
+    ``layers / 2 + 1`` layers.  Its layers cycle through ``kinds``; four taps, chunks of 1,024 positions, values as wide as
+    keys, low-rank pairs of 64; ``experts`` experts of which ``top`` are chosen, each as wide as the dense feed-forward
+    divided by ``top`` (as many active weights as the dense layer)."""
+    D, H, G = base["hidden_size"], base["num_attention_heads"], base["num_key_value_heads"]
+    hd = base.get("head_dim", D // H)
+    mixers = {
+        "attention": {"heads": H, "kv_heads": G, "dim": hd, "vdim": hd, "conv": 4, "mask": {"size": 1024}, "scale": hd ** -0.5,
+                      "rot": {"dims": hd, "base": 10000.0,
+                              "scaling": {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}}},
+        "channel_delta": {"heads": H, "kv_heads": H, "dim": hd, "vdim": hd, "conv": 4, "decay_rank": 64, "gate_rank": 64},
+    }
+    inner = max(1, layers // 2 - 1)
+    n = inner + 2
+    mlp = {"kind": "moe", "expert": {"ff": base["intermediate_size"] // top}, "router": {"experts": experts, "top": top, "scale": 2.5}}
+    return {"architecture": "Bulitar", "vocab": base["vocab_size"], "width": D, "embedding": {"scale": 12.0},
+            "norm": {"eps": 1e-5}, "loop": {"start": 1, "stop": 1 + inner, "times": 2},
+            "layers": [{"type": kinds[i % len(kinds)], "mixer": mixers[kinds[i % len(kinds)]], "mlp": mlp} for i in range(n)]}
+
+
 def run_design(name: str, sizes: str, layers: int, steps: int, warmup: int, only=None) -> int:
-    """Prefill of one 2,048-token prompt and decode at batch 1 / 8 / 64 over 2,048-token contexts for the Kudadra design:
-    all three kinds of layer in turn, each kind alone, and Qwen2 with as many layers of the same width, feed-forward,
+    """Prefill of one 2,048-token prompt and decode at batch 1 / 8 / 64 over 2,048-token contexts for another design:
+    its kinds of layer in turn, each kind alone, and Qwen2 with as many layer runs of the same width, feed-forward,
     heads and vocabulary.  Random weights drawn on the device; one JSON line, not the bench record."""
     import torch
     from lightllm_b200 import Engine
     from lightllm_b200.models import random_model_on_device
     base = dict(SIZES[sizes])
     base["num_hidden_layers"] = base["max_window_layers"] = layers
-    arms = {"qwen2": base, "kudadra": kudadra_config(base, layers)}
-    for kind in ("latent_attention", "attention", "retention"):
+    if name == "bulitar":
+        arms = {"qwen2": base, "bulitar": bulitar_config(base, layers)}
+        for kind in ("attention", "channel_delta"):
+            arms[f"bulitar/{kind}"] = bulitar_config(base, layers, (kind,))
+        arms["bulitar/every expert chosen"] = bulitar_config(base, layers, experts=2, top=2)
+    else:
+        arms = {"qwen2": base, "kudadra": kudadra_config(base, layers)}
+    for kind in ("latent_attention", "attention", "retention") if name == "kudadra" else ():
         arms[f"kudadra/{kind}"] = kudadra_config(base, layers, (kind,))
     if only:
         arms = {k: v for k, v in arms.items() if k in only.split(",")}
@@ -391,7 +419,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=QWEN25_05B["num_hidden_layers"])
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch (for profiling runs)")
-    ap.add_argument("--design", choices=["kudadra"], default=None,
+    ap.add_argument("--design", choices=["kudadra", "bulitar"], default=None,
                     help="measure another design beside Qwen2 at equal sizes (0.5B sizes, or --sizes; --layers, default 6; "
                          "--only names arms, e.g. kudadra,qwen2): a line of its own, not the bench record")
     ap.add_argument("--sizes", choices=["1.5b", "7b"], default=None,

@@ -207,6 +207,69 @@ def main(argv=None) -> int:
         run("head_linear_unfolded_up_projection", lambda: ops.head_linear(fused, 0, wq_up, ql), T * Hq * (hd + rank) * 2,
             2 * T * Hq * hd * rank)
 
+    # ---- the parts of the Bulitar layers: short convolution with rotation and head norms, the delta rule, routing --------
+    taps, Cc = 4, (Hq + 2 * Hkv) * hd
+    conv_w = rn(Cc, taps)
+    conv_src = rn(T, Cc, dtype=torch.bfloat16)
+    conv_state = torch.zeros((max(B, 1), Hq * hd * hd + (taps - 1) * (3 * Hq * hd)), device=dev)
+    spans1 = (z1, t1, z1, z1, 1)
+    segs = [ops.ConvSegment(0, Hq, hd, q_out, rotary_dim=hd, norm="rms", eps=1e-5),
+            ops.ConvSegment(Hq * hd, Hkv, hd, kc, to_cache=True, rotary_dim=hd, norm="rms", eps=1e-5),
+            ops.ConvSegment((Hq + Hkv) * hd, Hkv, hd, vc, to_cache=True)]
+    run("conv_prepare_rope_norm_cache", lambda: ops.conv_prepare(conv_src, 0, Cc, conv_w, segs, spans1, conv_state, Hq * hd * hd,
+                                                                 positions, inv_freq, 1.1), 2 * T * Cc * 2)
+    run("conv_tail_update", lambda: ops.conv_tail_update(conv_src, 0, Cc, taps, spans1, conv_state, Hq * hd * hd),
+        2 * (taps - 1) * Cc * 4)
+    dq, dk = rn(T, Hq * hd, s=hd ** -0.5), rn(T, Hq * hd, s=hd ** -0.5)
+    dv, dgate = rn(T, Hq * hd), torch.rand((T, Hq * hd), generator=g, device=dev) * 0.1 + 0.9
+    dbeta = rn(T, Hq, dtype=torch.bfloat16)
+    d_o = torch.empty((T, Hq * hd), device=dev)
+    run("delta_rule_prompt", lambda: ops.delta_rule(dq, dk, dv, dgate, dbeta, spans1, Hq, Hq, hd, hd, conv_state, 0, d_o),
+        T * Hq * hd * 5 * 4, 8 * T * Hq * hd * hd)
+    spansB = (rB, oB, pB, rB, B)
+    run("delta_rule_one_token", lambda: ops.delta_rule(dq[:B], dk[:B], dv[:B], dgate[:B], dbeta[:B], spansB, Hq, Hq, hd, hd,
+                                                       conv_state, 0, d_o[:B]), 2 * B * Hq * hd * hd * 4)
+    rank_lr = 64
+    lr_src = rn(T, rank_lr, dtype=torch.bfloat16)
+    w_up = rn(Hq * hd, rank_lr, dtype=torch.bfloat16, s=rank_lr ** -0.5)
+    rate, dt_b = torch.ones(Hq, device=dev), torch.zeros(Hq * hd, device=dev)
+    run("low_rank_up_decay", lambda: ops.low_rank_up(lr_src, 0, w_up, dgate, bias=dt_b, mode="decay", rate=rate),
+        T * (rank_lr * 2 + Hq * hd * 4), 2 * T * Hq * hd * rank_lr)
+    E, top = 8, 2
+    F = I // 2                      # eight experts of half the dense width, two chosen: as many active weights as the dense layer
+    w_router = rn(E, D, s=D ** -0.5)
+    r_ids = torch.empty((T, top), dtype=torch.int32, device=dev)
+    r_w, r_dense = torch.empty((T, top), device=dev), torch.empty((T, E), device=dev)
+    x_moe = rn(T, D, dtype=torch.bfloat16)
+    run("moe_route", lambda: ops.moe_route(x_moe, w_router, None, top, 2.5, r_ids, r_w, r_dense), T * D * 2 + T * E * 4,
+        2 * T * D * E)
+    act_moe = rn(T, E * F, dtype=torch.bfloat16)
+    run("moe_scale", lambda: ops.moe_scale(act_moe, r_dense, E, F), 2 * T * E * F * 2)
+    if ops.has_tcgen05() and T > 128:
+        from lightllm_b200.parts import linear as L
+        w_gu_all = rn(E * 2 * F, D, dtype=torch.bfloat16, s=D ** -0.5)
+        w_dn_all = rn(D, E * F, dtype=torch.bfloat16, s=(E * F) ** -0.5)
+        resid_m = rn(T, D)
+        run("moe_gate_up_all_experts", lambda: L.linear(x_moe, w_gu_all, None, L.SWIGLU, act_moe),
+            (T * D + E * 2 * F * D + T * E * F) * 2, 2 * T * E * 2 * F * D)
+        run("moe_down_all_experts", lambda: L.linear(act_moe, w_dn_all, None, L.RESIDUAL, residual=resid_m),
+            (T * E * F + D * E * F) * 2 + T * D * 8, 2 * T * D * E * F)
+    if ops.attention_tcgen05_supports(hd, page) and T > 128:
+        from lightllm_b200.engine.batch import cut_attention_rows, first_visible
+        from lightllm_b200.parts import linear as L
+        import numpy as np
+        chunk_c = 1024
+        rows_c = [(0, q0, -(-(min(q0 + 128, T) - (first_visible(q0, -chunk_c) // 128) * 128) // 128)) for q0 in range(0, T, 128)]
+        items, merges, parts = cut_attention_rows(rows_c, None, Hq, (2 if hd <= 64 else 1) * L.num_sms(dev))
+        arr = torch.from_numpy(np.asarray([t[1:] for t in items], dtype=np.int32).T.copy()).to(dev)
+        m = torch.from_numpy(np.asarray(merges, dtype=np.int32).reshape(-1, 4).T.copy()).to(dev)
+        cut = (arr[2], arr[3], arr[4], parts, m[0], m[1], m[2], m[3], len(merges)) if merges else (arr[2], arr[3], arr[4], 0, None, None, None, None, 0)
+        keys_seen = sum(p - first_visible(p, -chunk_c) + 1 for p in range(T))
+        run("paged_attention_tcgen05_chunks_of_1024",
+            lambda: ops.paged_attention_tcgen05(qp, kcp, vcp, op, arr[0].contiguous(), arr[1].contiguous(), len(items), sr, sl, sp, btp,
+                                                btp.shape[1], page, Hq, Hkv, hd, -chunk_c, 1 / math.sqrt(hd), cut=cut),
+            (2 * T * Hq * hd + 2 * T * Hkv * hd) * 2, 2 * 2 * Hq * hd * keys_seen)
+
     # ---- what a decode step of B requests over C keys runs --------------------------------------------------------------
     pages_per = -(-(C + 1) // page)
     kcd = rn(B * pages_per * page, Hkv, hd, dtype=torch.bfloat16)

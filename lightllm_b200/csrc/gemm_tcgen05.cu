@@ -67,6 +67,10 @@ struct GemmParams {
     __nv_bfloat16* k_cache;     // [slots, Hkv, 64]
     __nv_bfloat16* v_cache;
     int Hq, Hkv;
+    // grouped contraction (persistent kernel, single-CTA tiles): tile m of 128 rows multiplies by the weights of group
+    // tile_group[m], which are rows tile_group[m] * N .. + N - 1 of W (routed experts: rows sorted by expert, every
+    // expert's rows padded to whole tiles)
+    const int* tile_group;      // [ceil(M / 128)] or null
 };
 
 // Epilogue of one thread in the row-major orientation: token row m, CHUNK consecutive output features
@@ -539,7 +543,8 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
             for (int w = first_item; w < num_items; w += item_stride) {
                 const int t = w / splits, ks = w - t * splits;
                 const int a_row0 = (t % m_tiles) * ROWS_PER_TILE + (int)rank * TILE_M;
-                const int b_row0 = (t / m_tiles) * P_BN + (PAIR ? (int)rank * (P_BN / 2) : 0);
+                int b_row0 = (t / m_tiles) * P_BN + (PAIR ? (int)rank * (P_BN / 2) : 0);
+                if (!PAIR && p.tile_group) b_row0 += p.tile_group[t % m_tiles] * p.N;
                 const int kb0 = ks * p.kb_per_split, kb1 = min(nkb, kb0 + p.kb_per_split);
                 bool ok = true;
                 for (int kb = kb0; kb < kb1; kb += KPS, ++it) {
@@ -1050,6 +1055,38 @@ LLB_EXPORT int llb_gemm_tcgen05_glu(const void* A, const void* W, const float* b
         return dispatch_persistent<256>(epilogue, ma, mb, p, stream);
     }
     if ((rc = make_map(W, N, K, BN, &mb))) return rc;
+    return dispatch_persistent<128>(epilogue, ma, mb, p, stream);
+}
+
+// Grouped contraction: out[m, :] = epilogue(A[m, :] @ W[g(m)]^T) where W is [groups * N, K] (group g's weights are its
+// rows g * N .. g * N + N - 1) and g(m) = tile_group[m / 128]: the rows of A are sorted by group and every group's rows
+// begin at a multiple of 128.  M > 128; epilogues STORE, STORE_F32 and SWIGLU; no bias, no split along K.
+LLB_EXPORT int llb_gemm_tcgen05_grouped(const void* A, const void* W, void* out, int epilogue, int M, int N, int K,
+                                        int groups, const int* tile_group, int* error_flag, int glu_kind, float glu_alpha,
+                                        float glu_limit, float glu_up_shift, cudaStream_t stream) {
+    if (M == 0) return 0;
+    LLB_REQUIRE(M > 128 && N > 0 && K > 0 && groups > 0 && tile_group, "gemm_tcgen05_grouped: bad sizes M=%d N=%d K=%d", M, N, K);
+    LLB_REQUIRE(K % 8 == 0, "gemm_tcgen05_grouped: K=%d is not a multiple of 8 (rows must be 16-byte multiples for TMA)", K);
+    LLB_REQUIRE(((uintptr_t)A % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_tcgen05_grouped: operands must be 16-byte aligned");
+    LLB_REQUIRE(epilogue == LLB_EPI_STORE || epilogue == LLB_EPI_STORE_F32 || (epilogue == LLB_EPI_SWIGLU && N % 2 == 0),
+                "gemm_tcgen05_grouped: epilogue %d is not served (or N is odd under the GLU epilogue)", epilogue);
+    LLB_REQUIRE(out != nullptr && (long long)groups * N < (1ll << 31), "gemm_tcgen05_grouped: bad output or too many rows of W");
+    GemmParams p = {};
+    p.splits = 1;
+    p.out = out; p.M = M; p.N = N; p.K = K;
+    p.num_kb = llb_ceil_div(K, TILE_K);
+    p.kb_per_split = p.num_kb;
+    p.error_flag = error_flag;
+    p.glu = LlbGluArgs{glu_kind, glu_alpha, glu_limit, glu_up_shift};
+    p.tile_group = tile_group;
+    CUtensorMap ma, mb;
+    int rc;
+    if ((rc = make_map(A, M, K, TILE_M, &ma))) return rc;
+    if (N >= 2048) {
+        if ((rc = make_map(W, groups * N, K, 256, &mb))) return rc;
+        return dispatch_persistent<256>(epilogue, ma, mb, p, stream);
+    }
+    if ((rc = make_map(W, groups * N, K, 128, &mb))) return rc;
     return dispatch_persistent<128>(epilogue, ma, mb, p, stream);
 }
 

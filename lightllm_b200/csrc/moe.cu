@@ -96,7 +96,92 @@ __global__ void moe_scale_kernel(TA* __restrict__ act, const float* __restrict__
     }
 }
 
+// The (token, chosen expert) pairs in expert order, every expert's pairs padded to whole tiles of `align` rows: slot[i] is
+// the row of pair i (token i / top, its choice i % top), tile_group[m] the expert of tile m (0 for tiles behind the last
+// expert's).  One block: counts in shared memory, a serial walk over the experts, then a cursor per expert.  Which of an
+// expert's rows a pair gets depends on the order of the atomic adds; no result depends on it.
+__global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ ids, int pairs, int E, int align, int max_tiles,
+                                                        int* __restrict__ slot, int* __restrict__ tile_group) {
+    extern __shared__ int sh[];                  // count [E], cursor [E]
+    int* count = sh;
+    int* cursor = sh + E;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < pairs; i += blockDim.x) atomicAdd(&count[ids[i]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int tile = 0;
+        for (int e = 0; e < E; ++e) {
+            cursor[e] = tile * align;
+            const int n = (count[e] + align - 1) / align;
+            for (int j = 0; j < n && tile < max_tiles; ++j) tile_group[tile++] = e;
+        }
+        while (tile < max_tiles) tile_group[tile++] = 0;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < pairs; i += blockDim.x) slot[i] = atomicAdd(&cursor[ids[i]], 1);
+}
+
+// xs[slot[i], :] = x[i / top, :]
+template <typename TX>
+__global__ void __launch_bounds__(128) moe_gather_kernel(const TX* __restrict__ x, const int* __restrict__ slot, int top, int D,
+                                                         TX* __restrict__ xs) {
+    const int i = blockIdx.x;
+    const TX* src = x + (size_t)(i / top) * D;
+    TX* dst = xs + (size_t)slot[i] * D;
+    constexpr int V = 16 / sizeof(TX);
+    if (D % V == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)xs % 16 == 0) {
+        for (int d = threadIdx.x; d < D / V; d += blockDim.x)
+            reinterpret_cast<uint4*>(dst)[d] = reinterpret_cast<const uint4*>(src)[d];
+    } else {
+        for (int d = threadIdx.x; d < D; d += blockDim.x) dst[d] = src[d];
+    }
+}
+
+// residual[t, :] += sum_k weights[t, k] * y[slot[t * top + k], :], the choices added in their order
+__global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ slot,
+                                                          const float* __restrict__ weights, int top, int D,
+                                                          float* __restrict__ residual) {
+    const int t = blockIdx.x;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float acc = 0.0f;
+        for (int k = 0; k < top; ++k) acc = fmaf(weights[(size_t)t * top + k], y[(size_t)slot[(size_t)t * top + k] * D + d], acc);
+        residual[(size_t)t * D + d] += acc;
+    }
+}
+
 }  // namespace
+
+// ids int [T * top] -> slot int [T * top], tile_group int [max_tiles] (see moe_sort_kernel); max_tiles >= T * top / align + E.
+LLB_EXPORT int llb_moe_sort(const int* ids, int pairs, int E, int align, int max_tiles, int* slot, int* tile_group,
+                            cudaStream_t stream) {
+    if (pairs == 0) return 0;
+    LLB_REQUIRE(pairs > 0 && E > 0 && E <= 4096 && align > 0 && ids && slot && tile_group, "moe_sort: bad arguments");
+    LLB_REQUIRE(max_tiles >= pairs / align + E, "moe_sort: %d tiles cannot hold %d pairs of %d experts", max_tiles, pairs, E);
+    moe_sort_kernel<<<1, 1024, 2 * E * sizeof(int), stream>>>(ids, pairs, E, align, max_tiles, slot, tile_group);
+    return llb_check_launch("moe_sort");
+}
+
+// x [T, D] -> xs [rows, D] (same dtype): row slot[i] of xs is row i / top of x, for the T * top pairs.
+LLB_EXPORT int llb_moe_gather(const void* x, int dtype, const int* slot, int pairs, int top, int D, void* xs,
+                              cudaStream_t stream) {
+    if (pairs == 0) return 0;
+    LLB_REQUIRE(pairs > 0 && top > 0 && D > 0 && x && slot && xs, "moe_gather: bad arguments");
+    if (dtype == LLB_F32) moe_gather_kernel<float><<<pairs, 128, 0, stream>>>((const float*)x, slot, top, D, (float*)xs);
+    else if (dtype == LLB_BF16)
+        moe_gather_kernel<__nv_bfloat16><<<pairs, 128, 0, stream>>>((const __nv_bfloat16*)x, slot, top, D, (__nv_bfloat16*)xs);
+    else return llb_fail("moe_gather: unknown dtype %d", dtype);
+    return llb_check_launch("moe_gather");
+}
+
+// y float [rows, D], slot int [T * top], weights float [T, top], residual float [T, D] += the weighted rows.
+LLB_EXPORT int llb_moe_combine(const float* y, const int* slot, const float* weights, int T, int top, int D, float* residual,
+                               cudaStream_t stream) {
+    if (T == 0) return 0;
+    LLB_REQUIRE(T > 0 && top > 0 && D > 0 && y && slot && weights && residual, "moe_combine: bad arguments");
+    moe_combine_kernel<<<T, 256, 0, stream>>>(y, slot, weights, top, D, residual);
+    return llb_check_launch("moe_combine");
+}
 
 // x [T, D] float or bf16; w float [E, D]; correction float [E] or null; ids int [T, top]; weights float [T, top];
 // dense float [T, E].  softmax != 0: scores by a softmax over the experts, else by a sigmoid of each logit;

@@ -544,6 +544,59 @@ def moe_scale(act: torch.Tensor, dense: torch.Tensor, num_experts: int, width: i
     _check(lib().llb_moe_scale(_ptr(act), _dt(act), _f32(dense, "dense"), T, num_experts, width, _stream()))
 
 
+MOE_TILE_ROWS = 128          # rows of a tile of the grouped contraction: every expert's rows are padded to a multiple
+
+
+def moe_sorted_tiles(pairs: int, num_experts: int) -> int:
+    """Tiles that the (token, expert) pairs take at most once every expert's rows are padded to whole tiles."""
+    return -(-pairs // MOE_TILE_ROWS) + num_experts
+
+
+def moe_sort(ids: torch.Tensor, num_experts: int, slot: torch.Tensor, tile_group: torch.Tensor) -> None:
+    """ids int32 [T, top] -> slot int32 [T*top] (each pair's row in expert order, experts padded to whole tiles) and
+    tile_group int32 [moe_sorted_tiles(...)] (each tile's expert)."""
+    pairs = ids.numel()
+    if slot.numel() != pairs or tile_group.numel() < moe_sorted_tiles(pairs, num_experts):
+        raise KernelError("moe_sort: outputs do not fit")
+    _check(lib().llb_moe_sort(_i32(ids, "ids"), pairs, num_experts, MOE_TILE_ROWS, tile_group.numel(), _i32(slot, "slot"),
+                              _i32(tile_group, "tile_group"), _stream()))
+
+
+def moe_gather(x: torch.Tensor, slot: torch.Tensor, top: int, xs: torch.Tensor) -> None:
+    """xs[slot[i]] = x[i // top] for the T*top pairs."""
+    T, D = x.shape
+    if slot.numel() != T * top or xs.dtype != x.dtype or xs.shape[1] != D:
+        raise KernelError("moe_gather: sizes do not fit")
+    _check(lib().llb_moe_gather(_ptr(x), _dt(x), _i32(slot, "slot"), T * top, top, D, _ptr(xs), _stream()))
+
+
+def moe_combine(y: torch.Tensor, slot: torch.Tensor, weights: torch.Tensor, residual: torch.Tensor) -> None:
+    """residual[t] += sum_k weights[t, k] * y[slot[t*top + k]] in float."""
+    T, D = residual.shape
+    top = weights.shape[1]
+    if y.dtype != torch.float32 or y.shape[1] != D or slot.numel() != T * top or residual.dtype != torch.float32:
+        raise KernelError("moe_combine: sizes do not fit")
+    _check(lib().llb_moe_combine(_f32(y, "y"), _i32(slot, "slot"), _f32(weights, "weights"), T, top, D, _f32(residual, "residual"),
+                                 _stream()))
+
+
+def gemm_tcgen05_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, groups: int,
+                         tile_group: torch.Tensor, glu=None) -> None:
+    """out[m] = epilogue(a[m] @ w[g(m)]^T): ``w`` is [groups * N, K], the rows of ``a`` are sorted by group with every
+    group starting at a multiple of 128 rows, ``tile_group`` int32 names each 128-row tile's group.  bfloat16 operands,
+    more than 128 rows; epilogues STORE, STORE_F32, SWIGLU."""
+    M, K = a.shape
+    if w.shape[1] != K or w.shape[0] % groups or a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError(f"gemm_tcgen05_grouped: a {tuple(a.shape)} {a.dtype}, w {tuple(w.shape)} {w.dtype}, {groups} groups")
+    N = w.shape[0] // groups
+    cols = N // 2 if epilogue == EPI_SWIGLU else N
+    want = torch.float32 if epilogue == EPI_STORE_F32 else torch.bfloat16
+    if tuple(out.shape) != (M, cols) or out.dtype != want or tile_group.numel() < -(-M // MOE_TILE_ROWS):
+        raise KernelError("gemm_tcgen05_grouped: the output or the tiles' groups do not fit")
+    _check(lib().llb_gemm_tcgen05_grouped(_ptr(a), _ptr(w), _ptr(out), epilogue, M, N, K, groups, _i32(tile_group, "tile_group"),
+                                          _ptr(async_error_flag(a.device)), *_glu_args(glu), _stream()))
+
+
 DEPI_STORE_F32, DEPI_RESIDUAL, DEPI_SWIGLU, DEPI_ROPE_KV = 1, 2, 3, 4
 
 

@@ -21,16 +21,23 @@ class RoutedExperts(FeedForward):
     tensor that takes part in the choice only, or none), weights = the chosen experts' scores, divided by their sum
     with ``renormalize``, times ``route_scale``.
 
-    The experts run as two contractions over all of them: gate and up of every expert are the rows of one matrix
-    (interleaved pair by pair, the gated activation in the contraction's epilogue), the activations of expert e are
-    multiplied by w_e (zero for the experts a token did not choose) and the down matrices, side by side along the
-    inner dimension, add the weighted sum into the stream: ``sum_e w_e W_down_e a_e = [W_down_0 .. W_down_E-1]
-    [w_0 a_0; ..; w_E-1 a_E-1]``.  Every launch's shape follows from the step's token count alone, so steps replay
-    from CUDA graphs; the price is that every token meets every expert, ``num_experts / top`` times the arithmetic
-    that a grouped contraction over the chosen pairs would need."""
+    Two ways to run the experts, both with launches whose shapes follow from the step's token count alone, so that steps
+    replay from CUDA graphs:
+
+    * **every expert on every row** (few rows, float32, odd sizes): gate and up of all experts are the rows of one matrix
+      (interleaved pair by pair, the gated activation in the contraction's epilogue), the activations of expert e are
+      multiplied by w_e (zero for the experts a token did not choose) and the down matrices, side by side along the inner
+      dimension, add the weighted sum into the stream: ``sum_e w_e W_down_e a_e = [W_down_0 .. W_down_E-1] [w_0 a_0; ..;
+      w_E-1 a_E-1]``.  A decode step reads every expert's weights once, as it would anyway from about ``E / top`` rows on.
+    * **grouped** (bfloat16 on the tensor cores, from ``GROUPED_MIN_ROWS`` rows on where it needs less arithmetic): the
+      (token, expert) pairs are sorted by expert on the device, every expert's rows padded to whole tiles of 128, the rows
+      gathered, and two grouped contractions (each row tile takes its expert's weights) make the experts' outputs in
+      float, which are then added into the stream token by token with the routing weights, in the order of the choice.
+      The padded row count is bounded by ``T * top + 128 * E`` on the host, so nothing is read back from the device."""
 
     graph_safe = True
     accepts_lazy_norm = False
+    GROUPED = True               # False: every expert on every row, always (for comparisons)
 
     def __init__(self, prefix: str, hidden_size: int, intermediate_size: int, num_experts: int, top: int,
                  route_scale: float = 1.0, score: str = "sigmoid", renormalize: bool = False, correction: bool = False,
@@ -50,7 +57,7 @@ class RoutedExperts(FeedForward):
                       "correction": "correction"}
         self.names.update(names or {})
         self.weight_suffix, self.expert_prefix = weight_suffix, expert_prefix
-        self.w_router = self.correction = self.w_gate_up = self.w_down = None
+        self.w_router = self.correction = self.w_gate_up = self.w_down = self.w_down_rows = None
 
     def _e(self, e: int, which: str) -> str:
         return f"{self.prefix}.{self.expert_prefix}{e}.{self.names[which]}{self.weight_suffix}"
@@ -78,6 +85,8 @@ class RoutedExperts(FeedForward):
         self.w_gate_up = torch.stack([torch.stack([g.to(wdt), u.to(wdt)], dim=1).reshape(2 * I, D)
                                       for g, u in zip(gates, ups)]).reshape(E * 2 * I, D).contiguous()
         self.w_down = torch.cat([w.to(wdt) for w in downs], dim=1).contiguous()          # [D, E * I]
+        if wdt == torch.bfloat16 and dtype == torch.bfloat16 and self.top < E and D % 8 == 0 and I % 8 == 0:
+            self.w_down_rows = torch.cat(downs, dim=0).contiguous()                     # [E * D, I]: expert by expert
         L.reserve_fused_scratch(device, E * 2 * I)
 
     def route(self, x):
@@ -90,9 +99,35 @@ class RoutedExperts(FeedForward):
                       softmax=self.score == "softmax", renormalize=self.renormalize)
         return ids, weights, dense
 
+    def grouped_pays(self, rows: int) -> bool:
+        """Whether the grouped contractions need less arithmetic than every expert on every row: ``rows * top`` pairs plus
+        half a tile of padding an expert, against ``rows * experts``."""
+        return (self.GROUPED and self.w_down_rows is not None and ops.has_tcgen05()
+                and rows * self.top + 64 * self.num_experts < rows * self.num_experts
+                and rows * self.top + 128 * self.num_experts > 128)
+
+    def _forward_grouped(self, x, residual) -> None:
+        T, E, I, D = x.shape[0], self.num_experts, self.intermediate_size, self.hidden_size
+        ids, weights, _ = self.route(x)
+        tiles = ops.moe_sorted_tiles(T * self.top, E)
+        rows = tiles * ops.MOE_TILE_ROWS
+        slot = torch.empty(T * self.top, dtype=torch.int32, device=x.device)
+        tile_group = torch.empty(tiles, dtype=torch.int32, device=x.device)
+        ops.moe_sort(ids, E, slot, tile_group)
+        xs = torch.empty((rows, D), dtype=x.dtype, device=x.device)          # padding rows keep what the memory held:
+        ops.moe_gather(x, slot, self.top, xs)                               # a row's result depends on that row alone
+        act = torch.empty((rows, I), dtype=x.dtype, device=x.device)
+        ops.gemm_tcgen05_grouped(xs, self.w_gate_up, act, ops.EPI_SWIGLU, E, tile_group)
+        y = torch.empty((rows, D), dtype=torch.float32, device=x.device)
+        ops.gemm_tcgen05_grouped(act, self.w_down_rows, y, ops.EPI_STORE_F32, E, tile_group)
+        ops.moe_combine(y, slot, weights, residual)
+
     def forward(self, x, residual, ctx=None) -> None:
         if isinstance(x, LazyNorm):
             x = x.materialize()
+        if x.dtype == torch.bfloat16 and self.grouped_pays(x.shape[0]):
+            self._forward_grouped(x, residual)
+            return
         _, _, dense = self.route(x)
         act = L.linear(x, self.w_gate_up, None, L.SWIGLU)           # [T, E * I]
         ops.moe_scale(act, dense, self.num_experts, self.intermediate_size)

@@ -538,3 +538,40 @@ def test_greedy_generation_through_the_entry_point(tmp_path, name, dtype):
     eng.core.cache.check()
     assert eng.core.cache.free_slots == 3
     eng.core.runner.check_device_errors()
+
+
+@pytest.mark.parametrize("T,E,top,D,F", [(300, 8, 2, 64, 48), (1000, 5, 1, 128, 2056), (257, 16, 3, 96, 136)])
+def test_grouped_experts_equal_every_expert_on_every_row(T, E, top, D, F):
+    """The routed feed-forward on the grouped contractions (pairs sorted by expert, experts padded to whole tiles)
+    against the plain sum over the chosen experts and against the same part with every expert on every row; an expert
+    that no row chose and experts with more rows than a tile are among them."""
+    from lightllm_b200.parts.moe import RoutedExperts
+    if not ops.has_tcgen05():
+        pytest.skip("needs the tcgen05 contraction")
+    torch.manual_seed(T + E)
+    part = RoutedExperts("m", D, F, E, top, route_scale=2.5, correction=True, expert_prefix="e", weight_suffix="",
+                         names={"gate": "gate", "up": "up", "down": "down"})
+    W = {s.name: (torch.randn(s.shape) / (s.shape[-1] ** 0.5 if len(s.shape) == 2 else 1.0)).to(torch.bfloat16)
+         for s in part.weight_specs()}
+    W["m.correction"] = torch.randn(E).to(torch.bfloat16)
+    W["m.correction"][E - 1] = -50.0                      # the last expert is never chosen
+    part.bind({k: dev(v) for k, v in W.items()}, torch.bfloat16, DEV)
+    x = torch.randn(T, D).to(torch.bfloat16)
+    assert part.grouped_pays(T)
+    grouped, dense = torch.zeros(T, D, device=DEV), torch.zeros(T, D, device=DEV)
+    part.forward(dev(x), grouped)
+    ops.check_async_errors(DEV)
+    RoutedExperts.GROUPED = False
+    try:
+        part.forward(dev(x), dense)
+    finally:
+        RoutedExperts.GROUPED = True
+    Wd = {k: v.double() for k, v in W.items()}
+    want = P.moe(x.double(), Wd, "m", {"router": {"top": top, "scale": 2.5}})
+    # rows whose choice hangs on a close call are judged against the engine's own other path only
+    s = torch.sigmoid(x.double() @ Wd["m.router"].T) + Wd["m.correction"]
+    order = s.sort(-1, descending=True).values
+    sure = (order[:, top - 1] - order[:, top]) > 1e-3
+    assert sure.float().mean() > 0.9
+    close(grouped[sure.to(DEV)], want[sure], "bfloat16", "grouped experts against the plain sum", rel=2e-2)
+    close(grouped, dense.double().cpu(), "bfloat16", "grouped experts against every expert on every row", rel=2e-2)
