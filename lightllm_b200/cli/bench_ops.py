@@ -221,11 +221,13 @@ def main(argv=None) -> int:
     run("conv_tail_update", lambda: ops.conv_tail_update(conv_src, 0, Cc, taps, spans1, conv_state, Hq * hd * hd),
         2 * (taps - 1) * Cc * 4)
     dq, dk = rn(T, Hq * hd, s=hd ** -0.5), rn(T, Hq * hd, s=hd ** -0.5)
-    dv, dgate = rn(T, Hq * hd), torch.rand((T, Hq * hd), generator=g, device=dev) * 0.1 + 0.9
+    dv, dgate = rn(T, Hq * hd), torch.log(torch.rand((T, Hq * hd), generator=g, device=dev) * 0.1 + 0.9)
     dbeta = rn(T, Hq, dtype=torch.bfloat16)
     d_o = torch.empty((T, Hq * hd), device=dev)
-    run("delta_rule_prompt", lambda: ops.delta_rule(dq, dk, dv, dgate, dbeta, spans1, Hq, Hq, hd, hd, conv_state, 0, d_o),
-        T * Hq * hd * 5 * 4, 8 * T * Hq * hd * hd)
+    run("delta_rule_prompt_in_blocks", lambda: ops.delta_rule(dq, dk, dv, dgate, dbeta, spans1, Hq, Hq, hd, hd, conv_state, 0, d_o,
+                                                              blocked=True), T * Hq * hd * 5 * 4, 8 * T * Hq * hd * hd)
+    run("delta_rule_prompt_token_by_token", lambda: ops.delta_rule(dq, dk, dv, dgate, dbeta, spans1, Hq, Hq, hd, hd, conv_state, 0,
+                                                                   d_o), T * Hq * hd * 5 * 4, 8 * T * Hq * hd * hd)
     spansB = (rB, oB, pB, rB, B)
     run("delta_rule_one_token", lambda: ops.delta_rule(dq[:B], dk[:B], dv[:B], dgate[:B], dbeta[:B], spansB, Hq, Hq, hd, hd,
                                                        conv_state, 0, d_o[:B]), 2 * B * Hq * hd * hd * 4)
@@ -233,7 +235,7 @@ def main(argv=None) -> int:
     lr_src = rn(T, rank_lr, dtype=torch.bfloat16)
     w_up = rn(Hq * hd, rank_lr, dtype=torch.bfloat16, s=rank_lr ** -0.5)
     rate, dt_b = torch.ones(Hq, device=dev), torch.zeros(Hq * hd, device=dev)
-    run("low_rank_up_decay", lambda: ops.low_rank_up(lr_src, 0, w_up, dgate, bias=dt_b, mode="decay", rate=rate),
+    run("low_rank_up_decay", lambda: ops.low_rank_up(lr_src, 0, w_up, dgate, bias=dt_b, mode="log_decay", rate=rate),
         T * (rank_lr * 2 + Hq * hd * 4), 2 * T * Hq * hd * rank_lr)
     E, top = 8, 2
     F = I // 2                      # eight experts of half the dense width, two chosen: as many active weights as the dense layer

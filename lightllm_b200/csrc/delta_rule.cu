@@ -13,8 +13,9 @@
 // span is walked in order by one block per (head, column block).
 //
 // Also here: the small second projection of a low-rank pair (x W1^T) W2^T from columns of a fused first projection,
-// with what follows it in float: nothing, a sigmoid, or the decay exp(-rate_h * softplus(z + bias)).
+// with what follows it in float: nothing, a sigmoid, or the log decay -rate_h * softplus(z + bias).
 #include "common.cuh"
+#include "warp_mma.cuh"
 
 namespace {
 
@@ -24,7 +25,7 @@ struct DeltaParams {
     const float* q;            // [T, G, dim]
     const float* k;            // [T, G, dim]
     const float* v;            // [T, H, vdim]
-    const float* g;            // [T, H, dim] decay factors
+    const float* g;            // [T, H, dim] logarithms of the decay factors (<= 0)
     const void* beta;          // row t at beta + t * beta_stride elements: H values before the sigmoid
     long long beta_stride;
     int beta_dtype;
@@ -36,6 +37,10 @@ struct DeltaParams {
     long long state_stride, state_off;
     float* out;                // [T, H, vdim]
     int H, G, dim, vdim, EV;
+    int blocked;               // host: spans are walked in blocks of DELTA_STAGE tokens (delta_rule_blocked_kernel)
+    float* scratch;            // blocked: [max_blocks, H, delta_block_floats(dim)] what the first kernel leaves for the second
+    int max_blocks;            // blocked: at least sum over the spans of ceil(len / DELTA_STAGE)
+    int nr, dg;                // blocked: the second kernel's split of a column (rows a thread, threads a column)
 };
 
 template <int NR, int DG>
@@ -73,7 +78,7 @@ __global__ void __launch_bounds__(256) delta_rule_kernel(DeltaParams p) {
             const size_t row = (size_t)(row0 + c0 + tl);
             qs[tl * DPAD + at(d)] = p.q[(row * p.G + hk) * dim + d];
             ks[tl * DPAD + at(d)] = p.k[(row * p.G + hk) * dim + d];
-            gs[tl * DPAD + at(d)] = p.g[(row * p.H + h) * dim + d];
+            gs[tl * DPAD + at(d)] = expf(p.g[(row * p.H + h) * dim + d]);
         }
         for (int it = threadIdx.x; it < n * p.EV; it += blockDim.x) {
             const int tl = it / p.EV, cc = it - tl * p.EV;
@@ -132,6 +137,268 @@ __global__ void __launch_bounds__(256) delta_rule_kernel(DeltaParams p) {
     }
 }
 
+// The same recurrence over blocks of DELTA_STAGE tokens at a time, for spans long enough that walking them token by token
+// leaves the GPU waiting on one dependent chain per token.  With L_t the running sum of the log decays inside a block
+// (L_0 = 0) and S_0 the state before it, unrolling the recurrence gives
+//
+//     u_t = beta_t (v_t - S_0^T (e^{L_t} k_t) - sum_{s<t} A_ts u_s)        A_ts = sum_d k_t[d] k_s[d] e^{L_t[d] - L_s[d]}
+//     o_t = S_0^T (e^{L_t} q_t) + sum_{s<=t} M_ts u_s                       M_ts = sum_d q_t[d] k_s[d] e^{L_t[d] - L_s[d]}
+//     S_n = diag(e^{L_n}) S_0 + sum_s (e^{L_n - L_s} k_s) u_s^T
+//
+// A, M and the scaled rows belong to the head and the block of tokens, not to the state: a first kernel makes them for
+// all blocks of all spans side by side (every exponent is <= 0, so nothing overflows however fast a channel decays) and
+// leaves them in scratch; the second kernel walks a span's blocks in order, and for each block every column runs three
+// passes whose terms are independent across the block's tokens (the products with S_0, the read-out, the new state)
+// around one short forward substitution for u.  Block b of the step is block c of span s when the spans before s hold
+// b - c blocks: both kernels count the same way, so no list of blocks is needed from the host.
+constexpr int DELTA_PAIRS = DELTA_STAGE * (DELTA_STAGE + 1) / 2;
+
+// Floats that the first kernel leaves per (block of tokens, head), already in the second kernel's shared-memory layout:
+// three matrices [C][dpad] (a row's `dim` numbers in dg groups of nr, each padded by 4), one row [dpad], then A and M.
+__host__ __device__ inline long long delta_block_floats(int dpad) {
+    return 3ll * DELTA_STAGE * dpad + dpad + 2 * DELTA_STAGE * DELTA_STAGE;
+}
+
+__global__ void __launch_bounds__(256) delta_blocks_prepare_kernel(DeltaParams p, int num_spans) {
+    extern __shared__ __align__(16) float sm[];
+    constexpr int C = DELTA_STAGE;
+    const int dim = p.dim, h = blockIdx.y;
+    const int RS = dim + 1;                      // row pitch: the rows of a warp's pairs on different banks
+    int span = 0, c = blockIdx.x;
+    while (span < num_spans) {
+        const int blocks = (p.span_len[span] + C - 1) / C;
+        if (c < blocks) break;
+        c -= blocks;
+        ++span;
+    }
+    if (span >= num_spans) return;
+    const int len = p.span_len[span], row0 = p.span_row[span] + c * C;
+    const int n = min(C, len - c * C);
+    const int hk = h / (p.H / p.G);
+    float* kr = sm;                              // [C][RS]    k_t
+    float* qr = kr + C * RS;                     // [C][RS]    q_t
+    float* Ls = qr + C * RS;                     // [C][RS]    log decays, then their running sums L_t
+    const int nr = p.nr, padded = p.nr + (p.dg > 1 ? 4 : 0), dpad = p.dg * padded;
+    float* dst = p.scratch + ((size_t)blockIdx.x * p.H + h) * delta_block_floats(dpad);
+    float* Qb = dst;                             // [C][dpad]  e^{L_t} q_t
+    float* Kb = Qb + C * dpad;                   // [C][dpad]  e^{L_t} k_t
+    float* Kp = Kb + C * dpad;                   // [C][dpad]  e^{L_n - L_t} k_t
+    float* GC = Kp + C * dpad;                   // [dpad]     e^{L_n}
+    float* As = GC + dpad;                       // [C][C]     A_ts (s < t), else 0
+    float* Ms = As + C * C;                      // [C][C]     M_ts (s <= t), else 0
+    for (int it = threadIdx.x; it < C * dim; it += blockDim.x) {
+        const int tl = it / dim, d = it - tl * dim;
+        const size_t row = (size_t)(row0 + tl);
+        const bool in = tl < n;
+        kr[tl * RS + d] = in ? p.k[(row * p.G + hk) * dim + d] : 0.0f;
+        qr[tl * RS + d] = in ? p.q[(row * p.G + hk) * dim + d] : 0.0f;
+        Ls[tl * RS + d] = in ? p.g[(row * p.H + h) * dim + d] : 0.0f;
+    }
+    __syncthreads();
+    for (int d = threadIdx.x; d < dim; d += blockDim.x) {          // running sums of the log decays
+        float run = 0.0f;
+        for (int tl = 0; tl < C; ++tl) {
+            run += Ls[tl * RS + d];
+            Ls[tl * RS + d] = run;
+        }
+    }
+    __syncthreads();
+    for (int it = threadIdx.x; it < C * dim; it += blockDim.x) {
+        const int tl = it / dim, d = it - tl * dim;
+        const float L = Ls[tl * RS + d], Ln = Ls[(C - 1) * RS + d];          // rows past n add nothing: L stays L_n
+        const float eL = expf(L);
+        const int col = (d / nr) * padded + d % nr;
+        Kb[tl * dpad + col] = eL * kr[tl * RS + d];
+        Qb[tl * dpad + col] = eL * qr[tl * RS + d];
+        Kp[tl * dpad + col] = expf(Ln - L) * kr[tl * RS + d];
+        if (tl == 0) GC[col] = expf(Ln);
+    }
+    for (int it = threadIdx.x; it < (C + 1) * dpad; it += blockDim.x) {          // the padding is zero
+        const int col = it % dpad, tl = it / dpad;
+        if (col % padded >= nr || (col / padded) * nr + col % padded >= dim) {
+            if (tl < C) Qb[it] = Kb[it] = Kp[it] = 0.0f;
+            else GC[col] = 0.0f;
+        }
+    }
+    for (int pr = threadIdx.x; pr < C * C; pr += blockDim.x) {
+        const int t = pr / C, s = pr - t * C;
+        if (s > t) As[pr] = Ms[pr] = 0.0f;
+    }
+    for (int pr = threadIdx.x; pr < DELTA_PAIRS; pr += blockDim.x) {          // the pairs s <= t, packed: no idle lanes
+        int t = (int)((sqrtf(8.0f * pr + 1.0f) - 1.0f) * 0.5f);
+        while (t * (t + 1) / 2 > pr) --t;
+        while ((t + 1) * (t + 2) / 2 <= pr) ++t;
+        const int s = pr - t * (t + 1) / 2;
+        float a = 0.0f, m = 0.0f;
+        if (t < n) {
+            for (int d = 0; d < dim; ++d) {
+                const float w = kr[s * RS + d] * expf(Ls[t * RS + d] - Ls[s * RS + d]);
+                a = fmaf(kr[t * RS + d], w, a);
+                m = fmaf(qr[t * RS + d], w, m);
+            }
+        }
+        As[t * C + s] = s < t ? a : 0.0f;
+        Ms[t * C + s] = m;
+    }
+}
+
+template <int NR, int DG>
+__global__ void __launch_bounds__(64) delta_rule_blocked_kernel(DeltaParams p) {
+    extern __shared__ __align__(16) float sm[];
+    constexpr int C = DELTA_STAGE;
+    constexpr int PADF = DG > 1 ? 4 : 0;
+    constexpr int DPAD = DG * (NR + PADF);
+    const int span = blockIdx.x, h = blockIdx.y;
+    const int dim = p.dim, vdim = p.vdim;
+    const int len = p.span_len[span], row0 = p.span_row[span], pos0 = p.span_pos[span];
+    int first_block = 0;                         // of this span among the step's blocks (as the first kernel counts them)
+    for (int s = 0; s < span; ++s) first_block += (p.span_len[s] + C - 1) / C;
+    constexpr int BLOCK_FLOATS = 3 * C * DPAD + DPAD + 2 * C * C;          // = delta_block_floats(DPAD): one copy of 16-byte pieces
+    const int stage_floats = BLOCK_FLOATS + C * p.EV + C;                  // + v [C][EV] and beta [C]
+    const int stage_pitch = (stage_floats + 3) & ~3;
+    const int dg = threadIdx.x % DG, el = threadIdx.x / DG;
+    const int e = blockIdx.z * p.EV + el;
+    const bool live = el < p.EV && e < vdim;
+    float* slot = p.state + (long long)p.span_slot[span] * p.state_stride + p.state_off + (size_t)h * dim * vdim;
+
+    float S[NR];
+#pragma unroll
+    for (int j = 0; j < NR; ++j) {
+        const int d = dg * NR + j;
+        S[j] = (pos0 > 0 && live && d < dim) ? slot[(size_t)d * vdim + e] : 0.0f;
+    }
+    // Two stages in shared memory: while a block of tokens is worked on, the next one's matrices arrive by cp.async and its
+    // values and betas wait in registers.
+    auto fetch = [&](int blk, int stage) {
+        const float* src = p.scratch + ((size_t)blk * p.H + h) * BLOCK_FLOATS;
+        const uint32_t dst = (uint32_t)__cvta_generic_to_shared(sm + stage * stage_pitch);
+        for (int i = threadIdx.x; i < BLOCK_FLOATS / 4; i += blockDim.x) wm::cp_async16(dst + i * 16, src + i * 4, true);
+        wm::cp_async_commit();
+    };
+    constexpr int VPT = (C * 64 / DG + 63) / 64;                           // values a thread carries for the next block
+    float vnext[VPT], bnext = 0.0f;
+    auto load_vb = [&](int c0) {
+        const int n = min(C, len - c0);
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int it = threadIdx.x + i * blockDim.x;
+            const int tl = it / p.EV, cc = it - tl * p.EV;
+            const int ee = blockIdx.z * p.EV + cc;
+            vnext[i] = (it < C * p.EV && tl < n && ee < vdim) ? p.v[((size_t)(row0 + c0 + tl) * p.H + h) * vdim + ee] : 0.0f;
+        }
+        bnext = 0.0f;
+        if (threadIdx.x < n) {
+            const size_t at_b = (size_t)(row0 + c0 + threadIdx.x) * p.beta_stride + h;
+            const float z = p.beta_dtype == LLB_F32 ? ((const float*)p.beta)[at_b]
+                                                    : __bfloat162float(((const __nv_bfloat16*)p.beta)[at_b]);
+            bnext = 1.0f / (1.0f + expf(-z));
+        }
+    };
+    auto store_vb = [&](int stage) {
+        float* vsn = sm + stage * stage_pitch + BLOCK_FLOATS;
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int it = threadIdx.x + i * blockDim.x;
+            if (it < C * p.EV) vsn[it] = vnext[i];
+        }
+        if (threadIdx.x < C) vsn[C * p.EV + threadIdx.x] = bnext;
+    };
+    fetch(first_block, 0);
+    load_vb(0);
+    store_vb(0);
+    for (int c0 = 0, blk = first_block, stage = 0; c0 < len; c0 += C, ++blk, stage ^= 1) {
+        const int n = min(C, len - c0);
+        const bool more = c0 + C < len;
+        if (more) {
+            fetch(blk + 1, stage ^ 1);          // (the stage it lands in was last read before the barrier that ended the block before)
+            load_vb(c0 + C);
+            wm::cp_async_wait<1>();
+        } else {
+            wm::cp_async_wait<0>();
+        }
+        __syncthreads();
+        const float* Qb = sm + stage * stage_pitch;          // [C][DPAD]
+        const float* Kb = Qb + C * DPAD;                       // [C][DPAD]
+        const float* Kp = Kb + C * DPAD;                       // [C][DPAD]
+        const float* GC = Kp + C * DPAD;                       // [DPAD]
+        const float* As = GC + DPAD;                           // [C][C]
+        const float* Ms = As + C * C;                          // [C][C]
+        const float* vs = Ms + C * C;                          // [C][EV]
+        const float* bs = vs + C * p.EV;                       // [C]
+        // what the state before the block gives every token: w_t = v_t - S_0^T (e^{L_t} k_t), o_t = S_0^T (e^{L_t} q_t)
+        float w[C], o[C];
+#pragma unroll
+        for (int t = 0; t < C; ++t) {
+            const float4* k4p = reinterpret_cast<const float4*>(Kb + t * DPAD + dg * (NR + PADF));
+            const float4* q4p = reinterpret_cast<const float4*>(Qb + t * DPAD + dg * (NR + PADF));
+            float a0 = 0.0f, a1 = 0.0f, b0 = 0.0f, b1 = 0.0f;
+#pragma unroll
+            for (int j = 0; j < NR; j += 4) {
+                const float4 k4 = k4p[j >> 2], q4 = q4p[j >> 2];
+                a0 = fmaf(S[j], k4.x, a0); a1 = fmaf(S[j + 1], k4.y, a1);
+                a0 = fmaf(S[j + 2], k4.z, a0); a1 = fmaf(S[j + 3], k4.w, a1);
+                b0 = fmaf(S[j], q4.x, b0); b1 = fmaf(S[j + 1], q4.y, b1);
+                b0 = fmaf(S[j + 2], q4.z, b0); b1 = fmaf(S[j + 3], q4.w, b1);
+            }
+            w[t] = a0 + a1;
+            o[t] = b0 + b1;
+        }
+#pragma unroll
+        for (int t = 0; t < C; ++t) {
+#pragma unroll
+            for (int sh = DG >> 1; sh > 0; sh >>= 1) {
+                w[t] += __shfl_xor_sync(0xffffffffu, w[t], sh);
+                o[t] += __shfl_xor_sync(0xffffffffu, o[t], sh);
+            }
+            w[t] = (el < p.EV ? vs[t * p.EV + el] : 0.0f) - w[t];
+        }
+        // forward substitution (every lane of a column computes the same u), and the read-out's part from inside the block
+        float u[C];
+#pragma unroll
+        for (int t = 0; t < C; ++t) {
+            float acc = w[t];
+#pragma unroll
+            for (int s = 0; s < t; ++s) acc = fmaf(-As[t * C + s], u[s], acc);
+            u[t] = bs[t] * acc;
+        }
+#pragma unroll
+        for (int t = 0; t < C; ++t) {
+            float acc = o[t];
+#pragma unroll
+            for (int s = 0; s <= t; ++s) acc = fmaf(Ms[t * C + s], u[s], acc);
+            if (live && dg == 0 && t < n) p.out[((size_t)(row0 + c0 + t) * p.H + h) * vdim + e] = acc;
+        }
+        // the state after the block
+        {
+            const float4* g4p = reinterpret_cast<const float4*>(GC + dg * (NR + PADF));
+#pragma unroll
+            for (int j = 0; j < NR; j += 4) {
+                const float4 g4 = g4p[j >> 2];
+                S[j] *= g4.x; S[j + 1] *= g4.y; S[j + 2] *= g4.z; S[j + 3] *= g4.w;
+            }
+#pragma unroll
+            for (int t = 0; t < C; ++t) {
+                const float4* k4p = reinterpret_cast<const float4*>(Kp + t * DPAD + dg * (NR + PADF));
+#pragma unroll
+                for (int j = 0; j < NR; j += 4) {
+                    const float4 k4 = k4p[j >> 2];
+                    S[j] = fmaf(k4.x, u[t], S[j]); S[j + 1] = fmaf(k4.y, u[t], S[j + 1]);
+                    S[j + 2] = fmaf(k4.z, u[t], S[j + 2]); S[j + 3] = fmaf(k4.w, u[t], S[j + 3]);
+                }
+            }
+        }
+        if (more) store_vb(stage ^ 1);
+        __syncthreads();          // every thread has read this stage: the block after next may land in it
+    }
+    if (live) {
+#pragma unroll
+        for (int j = 0; j < NR; ++j) {
+            const int d = dg * NR + j;
+            if (d < dim) slot[(size_t)d * vdim + e] = S[j];
+        }
+    }
+}
+
 template <int NR, int DG>
 int launch_delta(const DeltaParams& p0, int num_spans, cudaStream_t stream) {
     DeltaParams p = p0;
@@ -141,6 +408,34 @@ int launch_delta(const DeltaParams& p0, int num_spans, cudaStream_t stream) {
     const size_t smem = (size_t)(3 * DELTA_STAGE * DG * (NR + PADF) + DELTA_STAGE * p.EV + DELTA_STAGE) * sizeof(float);
     const int threads = ((p.EV * DG + 31) / 32) * 32;
     const dim3 grid(num_spans, p.H, (p.vdim + p.EV - 1) / p.EV);
+    if (p.blocked) {
+        // two warps a block: what paces a block is its own chain of blocks of tokens, so the columns are spread over as
+        // many multiprocessors as there are; the first kernel has made what all of a head's columns share
+        constexpr int C = DELTA_STAGE;
+        const int cols_b = 64 / DG;
+        p.EV = p.vdim < cols_b ? p.vdim : cols_b;
+        const int threads_b = ((p.EV * DG + 31) / 32) * 32;
+        const dim3 grid_b(num_spans, p.H, (p.vdim + p.EV - 1) / p.EV);
+        const size_t pre_bytes = (size_t)3 * C * (p.dim + 1) * sizeof(float);
+        if (pre_bytes > 48 * 1024) {
+            const cudaError_t e = cudaFuncSetAttribute(delta_blocks_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                       (int)pre_bytes);
+            if (e != cudaSuccess) return llb_fail("delta_rule: %s", cudaGetErrorString(e));
+        }
+        p.nr = NR; p.dg = DG;
+        delta_blocks_prepare_kernel<<<dim3(p.max_blocks, p.H), 256, pre_bytes, stream>>>(p, num_spans);
+        int rc = llb_check_launch("delta_blocks_prepare");
+        if (rc) return rc;
+        const size_t stage = ((size_t)delta_block_floats(DG * (NR + PADF)) + C * p.EV + C + 3) & ~(size_t)3;
+        const size_t bytes = 2 * stage * sizeof(float);
+        if (bytes > 48 * 1024) {
+            const cudaError_t e = cudaFuncSetAttribute(delta_rule_blocked_kernel<NR, DG>,
+                                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+            if (e != cudaSuccess) return llb_fail("delta_rule: %s", cudaGetErrorString(e));
+        }
+        delta_rule_blocked_kernel<NR, DG><<<grid_b, threads_b, bytes, stream>>>(p);
+        return llb_check_launch("delta_rule_blocked");
+    }
     if (smem > 48 * 1024) {
         const cudaError_t e = cudaFuncSetAttribute(delta_rule_kernel<NR, DG>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return llb_fail("delta_rule: %s", cudaGetErrorString(e));
@@ -160,53 +455,79 @@ struct LowRankParams {
     int mode;
 };
 
+// A block takes LR_ROWS rows of x (their R inputs in shared memory, padded to a multiple of 4) and 256 outputs; a thread
+// owns one output for all the block's rows, so a weight is loaded once for LR_ROWS products and the inputs come as
+// 16-byte broadcast reads.
+constexpr int LR_ROWS = 16;
+
 template <typename TX, typename TW, typename TO>
-__global__ void __launch_bounds__(256) low_rank_up_kernel(LowRankParams p) {
-    extern __shared__ float xs[];                    // [R]
-    const int t = blockIdx.y;
-    const TX* xr = (const TX*)p.x + (size_t)t * p.x_stride + p.x_off;
-    for (int r = threadIdx.x; r < p.R; r += blockDim.x) xs[r] = llb_to_float(xr[r]);
+__global__ void __launch_bounds__(256) low_rank_up_kernel(LowRankParams p, int T) {
+    extern __shared__ __align__(16) float xs[];      // [LR_ROWS][R4]
+    const int R4 = (p.R + 3) & ~3;
+    const int t0 = blockIdx.y * LR_ROWS;
+    const int rows = min(LR_ROWS, T - t0);
+    for (int i = threadIdx.x; i < LR_ROWS * R4; i += blockDim.x) {
+        const int tl = i / R4, r = i - tl * R4;
+        xs[i] = (tl < rows && r < p.R) ? llb_to_float(((const TX*)p.x)[(size_t)(t0 + tl) * p.x_stride + p.x_off + r]) : 0.0f;
+    }
     __syncthreads();
     const int n = blockIdx.x * blockDim.x + threadIdx.x;
     if (n >= p.N) return;
     const TW* wr = (const TW*)p.w + (size_t)n * p.R;
-    float a0 = 0.0f, a1 = 0.0f;
-    int r = 0;
-    for (; r + 1 < p.R; r += 2) {
-        a0 = fmaf(xs[r], llb_to_float(wr[r]), a0);
-        a1 = fmaf(xs[r + 1], llb_to_float(wr[r + 1]), a1);
+    float acc[LR_ROWS];
+#pragma unroll
+    for (int tl = 0; tl < LR_ROWS; ++tl) acc[tl] = 0.0f;
+    for (int r = 0; r < R4; r += 4) {
+        float w4[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) w4[j] = r + j < p.R ? llb_to_float(wr[r + j]) : 0.0f;
+#pragma unroll
+        for (int tl = 0; tl < LR_ROWS; ++tl) {
+            const float4 x4 = *reinterpret_cast<const float4*>(xs + tl * R4 + r);
+            acc[tl] = fmaf(x4.x, w4[0], acc[tl]);
+            acc[tl] = fmaf(x4.y, w4[1], acc[tl]);
+            acc[tl] = fmaf(x4.z, w4[2], acc[tl]);
+            acc[tl] = fmaf(x4.w, w4[3], acc[tl]);
+        }
     }
-    if (r < p.R) a0 = fmaf(xs[r], llb_to_float(wr[r]), a0);
-    float z = a0 + a1;
-    if (p.bias) z += p.bias[n];
-    if (p.mode == 1) {
-        z = 1.0f / (1.0f + expf(-z));
-    } else if (p.mode == 2) {
-        const float sp = z > 20.0f ? z : log1pf(expf(z));
-        z = expf(-p.rate[n / p.per_rate] * sp);
+    const float bias = p.bias ? p.bias[n] : 0.0f;
+    const float rate = p.mode == 2 ? p.rate[n / p.per_rate] : 0.0f;
+#pragma unroll
+    for (int tl = 0; tl < LR_ROWS; ++tl) {
+        if (tl >= rows) break;
+        float z = acc[tl] + bias;
+        if (p.mode == 1) {
+            z = 1.0f / (1.0f + expf(-z));
+        } else if (p.mode == 2) {
+            const float sp = z > 20.0f ? z : log1pf(expf(z));
+            z = -rate * sp;
+        }
+        ((TO*)p.out)[(size_t)(t0 + tl) * p.N + n] = llb_from_float<TO>(z);
     }
-    ((TO*)p.out)[(size_t)t * p.N + n] = llb_from_float<TO>(z);
 }
 
 template <typename TX, typename TW>
 int launch_low_rank(const LowRankParams& p, int T, int out_dtype, cudaStream_t stream) {
-    const dim3 grid((p.N + 255) / 256, T);
-    const size_t smem = (size_t)p.R * sizeof(float);
-    if (out_dtype == LLB_F32) low_rank_up_kernel<TX, TW, float><<<grid, 256, smem, stream>>>(p);
-    else low_rank_up_kernel<TX, TW, __nv_bfloat16><<<grid, 256, smem, stream>>>(p);
+    const dim3 grid((p.N + 255) / 256, (T + LR_ROWS - 1) / LR_ROWS);
+    const size_t smem = (size_t)LR_ROWS * ((p.R + 3) & ~3) * sizeof(float);
+    if (out_dtype == LLB_F32) low_rank_up_kernel<TX, TW, float><<<grid, 256, smem, stream>>>(p, T);
+    else low_rank_up_kernel<TX, TW, __nv_bfloat16><<<grid, 256, smem, stream>>>(p, T);
     return llb_check_launch("low_rank_up");
 }
 
 }  // namespace
 
-// q, k float [T, G, dim]; v float [T, H, vdim]; g float [T, H, dim] (the decay factors themselves); beta: the H values
+// q, k float [T, G, dim]; v float [T, H, vdim]; g float [T, H, dim] (the logarithms of the decay factors, <= 0); blocked != 0
+// walks the spans in blocks of tokens (for steps with long spans; the result is the same recurrence) and needs scratch of
+// llb_delta_rule_scratch_floats(max_blocks, H, dim) floats, max_blocks >= sum over spans of ceil(len / 16) (T / 16 +
+// num_spans always suffices); beta: the H values
 // before the sigmoid of row t at beta + t * beta_stride (float or bf16); the spans of the step; state: float base of the
 // state plane, state_stride floats a slot, a slot's S [H, dim, vdim] at state_off; out float [T, H, vdim].
 LLB_EXPORT int llb_delta_rule(const float* q, const float* k, const float* v, const float* g, const void* beta,
                               long long beta_stride, int beta_dtype, const int* span_row, const int* span_len,
                               const int* span_pos, const int* span_slot, int num_spans, int H, int G, int dim, int vdim,
-                              float* state, long long state_stride, long long state_off, float* out,
-                              cudaStream_t stream) {
+                              float* state, long long state_stride, long long state_off, float* out, int blocked,
+                              float* scratch, int max_blocks, cudaStream_t stream) {
     if (num_spans == 0) return 0;
     LLB_REQUIRE(q && k && v && g && beta && state && out && span_row && span_len && span_pos && span_slot,
                 "delta_rule: bad arguments");
@@ -217,7 +538,16 @@ LLB_EXPORT int llb_delta_rule(const float* q, const float* k, const float* v, co
     p.q = q; p.k = k; p.v = v; p.g = g; p.beta = beta; p.beta_stride = beta_stride; p.beta_dtype = beta_dtype;
     p.span_row = span_row; p.span_len = span_len; p.span_pos = span_pos; p.span_slot = span_slot;
     p.state = state; p.state_stride = state_stride; p.state_off = state_off; p.out = out;
-    p.H = H; p.G = G; p.dim = dim; p.vdim = vdim; p.EV = 0;
+    p.H = H; p.G = G; p.dim = dim; p.vdim = vdim; p.EV = 0; p.blocked = blocked;
+    p.scratch = scratch; p.max_blocks = max_blocks;
+    LLB_REQUIRE(!blocked || (scratch && max_blocks > 0), "delta_rule: the blocked walk needs scratch");
+    if (blocked) {          // more threads a column: what paces a block of tokens is a warp's own instruction chain
+        if (dim <= 16) return launch_delta<4, 4>(p, num_spans, stream);
+        if (dim <= 32) return launch_delta<8, 4>(p, num_spans, stream);
+        if (dim <= 64) return launch_delta<8, 8>(p, num_spans, stream);
+        if (dim <= 128) return launch_delta<16, 8>(p, num_spans, stream);
+        return launch_delta<32, 8>(p, num_spans, stream);
+    }
     if (dim <= 16) return launch_delta<16, 1>(p, num_spans, stream);
     if (dim <= 32) return launch_delta<16, 2>(p, num_spans, stream);
     if (dim <= 64) return launch_delta<16, 4>(p, num_spans, stream);
@@ -225,16 +555,22 @@ LLB_EXPORT int llb_delta_rule(const float* q, const float* k, const float* v, co
     return launch_delta<32, 8>(p, num_spans, stream);
 }
 
+LLB_EXPORT long long llb_delta_rule_scratch_floats(int max_blocks, int H, int dim) {
+    const int nr = dim <= 16 ? 4 : dim <= 64 ? 8 : dim <= 128 ? 16 : 32;          // as llb_delta_rule picks them
+    const int dg = dim <= 32 ? 4 : 8;
+    return (long long)max_blocks * H * delta_block_floats(dg * (nr + 4));
+}
+
 // out[t, n] = f(sum_r x[t, x_off + r] * w[n, r] + bias[n]) for T rows of x (row stride x_stride elements, float or bf16),
 // w [N, R] float or bf16, bias float [N] or null, out [T, N] float or bf16.  mode 0: f = identity; 1: sigmoid;
-// 2: exp(-rate[n / per_rate] * softplus(.)), rate float [N / per_rate].
+// 2: -rate[n / per_rate] * softplus(.), the logarithm of a decay factor, rate float [N / per_rate].
 LLB_EXPORT int llb_low_rank_up(const void* x, int x_dtype, long long x_stride, int x_off, int T, int R, const void* w,
                                int w_dtype, int N, const float* bias, int mode, const float* rate, int per_rate,
                                void* out, int out_dtype, cudaStream_t stream) {
     if (T == 0 || N == 0) return 0;
     LLB_REQUIRE(T > 0 && R > 0 && N > 0 && x && w && out, "low_rank_up: bad arguments");
     LLB_REQUIRE(mode >= 0 && mode <= 2 && (mode != 2 || (rate && per_rate > 0)), "low_rank_up: bad mode %d", mode);
-    LLB_REQUIRE(R <= 8192, "low_rank_up: %d inputs; at most 8192", R);
+    LLB_REQUIRE(R <= 512, "low_rank_up: %d inputs; at most 512 (the first half of a low-rank pair is narrow)", R);
     LLB_REQUIRE(out_dtype == LLB_F32 || out_dtype == LLB_BF16, "low_rank_up: unknown output dtype %d", out_dtype);
     LowRankParams p;
     p.x = x; p.x_stride = x_stride; p.x_off = x_off; p.R = R; p.N = N; p.per_rate = per_rate; p.w = w; p.bias = bias;

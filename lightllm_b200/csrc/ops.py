@@ -477,10 +477,11 @@ def conv_tail_update(src: torch.Tensor, c0: int, channels: int, taps: int, ctx_s
 
 def delta_rule(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tensor, beta: torch.Tensor, ctx_spans,
                num_heads: int, num_qk_heads: int, head_dim: int, v_head_dim: int, state: torch.Tensor, state_off: int,
-               out: torch.Tensor) -> None:
+               out: torch.Tensor, blocked: bool = False) -> None:
     """The gated delta rule over every span (csrc/delta_rule.cu).  q, k float32 [T, G*dim]; v float32 [T, H*vdim]; g float32
-    [T, H*dim] decay factors; ``beta`` a [T, H] view (rows may be strided) of values before the sigmoid; the state
-    [H, dim, vdim] of a request lies ``state_off`` floats into its slot of ``state``; out float32 [T, H*vdim]."""
+    [T, H*dim] logarithms of the decay factors; ``beta`` a [T, H] view (rows may be strided) of values before the
+    sigmoid; the state [H, dim, vdim] of a request lies ``state_off`` floats into its slot of ``state``; out float32
+    [T, H*vdim].  ``blocked`` walks the spans in blocks of 16 tokens (for steps with long spans), else token by token."""
     T = q.shape[0]
     H, G, dim, vdim = num_heads, num_qk_heads, head_dim, v_head_dim
     for t, n, what in ((q, G * dim, "q"), (k, G * dim, "k"), (v, H * vdim, "v"), (g, H * dim, "g"), (out, H * vdim, "out")):
@@ -492,27 +493,32 @@ def delta_rule(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, g: torch.Tenso
     base, stride = _state_base(state)
     if state_off + H * dim * vdim > stride:
         raise KernelError("delta_rule: the state does not fit in a slot")
+    scratch, max_blocks = None, 0
+    if blocked:          # what the first kernel leaves for the second: bounded by the step's counts alone
+        max_blocks = T // 16 + num_spans
+        scratch = torch.empty(int(lib().llb_delta_rule_scratch_floats(max_blocks, H, dim)), dtype=torch.float32, device=q.device)
     _check(lib().llb_delta_rule(_ptr(q), _ptr(k), _ptr(v), _ptr(g), ctypes.c_void_p(beta.data_ptr()),
                                 ctypes.c_longlong(beta.stride(0)), _dt(beta), _i32(span_row, "span_row"),
                                 _i32(span_len, "span_len"), _i32(span_pos, "span_pos"), _i32(span_slot, "span_slot"),
                                 num_spans, H, G, dim, vdim, base, ctypes.c_longlong(stride), ctypes.c_longlong(state_off),
-                                _ptr(out), _stream()))
+                                _ptr(out), 1 if blocked else 0, _ptr(scratch), max_blocks, _stream()))
 
 
-LOW_RANK_MODES = {None: 0, "sigmoid": 1, "decay": 2}
+LOW_RANK_MODES = {None: 0, "sigmoid": 1, "log_decay": 2}
 
 
 def low_rank_up(x: torch.Tensor, x_off: int, w: torch.Tensor, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
                 mode=None, rate: Optional[torch.Tensor] = None) -> None:
     """out[t, n] = f(sum_r x[t, x_off + r] * w[n, r] + bias[n]) with float sums: the second half of a low-rank pair,
-    read from columns of a fused first projection.  ``mode`` None, ``"sigmoid"`` or ``"decay"``:
-    ``exp(-rate[h] * softplus(.))`` with ``rate`` float32 [H] and n = h * (N / H) + ...; out float32 or bfloat16 [T, N]."""
+    read from columns of a fused first projection.  ``mode`` None, ``"sigmoid"`` or ``"log_decay"``:
+    ``-rate[h] * softplus(.)`` (the logarithm of a decay factor) with ``rate`` float32 [H] and n = h * (N / H) + ...;
+    out float32 or bfloat16 [T, N]."""
     T, C = x.shape
     N, R = w.shape
     if x_off + R > C or tuple(out.shape) != (T, N):
         raise KernelError("low_rank_up: sizes do not fit")
     per = 1
-    if mode == "decay":
+    if mode == "log_decay":
         if rate is None or N % rate.numel():
             raise KernelError("low_rank_up: the decay mode needs one rate per head")
         per = N // rate.numel()

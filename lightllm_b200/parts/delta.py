@@ -105,11 +105,14 @@ class ChannelDeltaMixer(Mixer):
         ops.conv_tail_update(fused, 0, self.channels, self.conv_taps, spans, cache.state, tail_off)
         c = self.channels
         decay = torch.empty((T, H * hd), **f32)
-        ops.low_rank_up(fused, c + H, self.w_a2, decay, bias=self.dt_bias, mode="decay", rate=self.rate)
+        ops.low_rank_up(fused, c + H, self.w_a2, decay, bias=self.dt_bias, mode="log_decay", rate=self.rate)
         gate = torch.empty((T, H * vd), dtype=x.dtype, device=x.device)
         ops.low_rank_up(fused, c + H + self.decay_rank, self.w_g2, gate)
         o = torch.empty((T, H * vd), **f32)
-        ops.delta_rule(q, k, v, decay, fused[:, c: c + H], spans, H, G, hd, vd, cache.state, 0, o)
+        # a step with portions of prompts walks its spans in blocks of tokens; a step of single tokens token by token
+        # (the choice follows from what a CUDA graph's key holds)
+        ops.delta_rule(q, k, v, decay, fused[:, c: c + H], spans, H, G, hd, vd, cache.state, 0, o,
+                       blocked=not ctx.decode_only)
         gated = torch.empty((T, H * vd), dtype=x.dtype, device=x.device)
         ops.head_gate(o, gate, gated, H, vd, False, "sigmoid", unit_rms=True, eps=self.norm_eps, norm_weight=self.norm_w)
         L.linear(gated, self.w_o, None, L.RESIDUAL, residual=residual)

@@ -132,8 +132,9 @@ def test_short_convolution_with_rotation_and_head_norms(dtype, taps):
         assert torch.equal(tail, proj["a"][23 - (taps - 1):, :C].float())
 
 
+@pytest.mark.parametrize("blocked", [False, True])
 @pytest.mark.parametrize("H,G,d,e", [(3, 1, 12, 20), (2, 2, 24, 9), (4, 2, 64, 64), (2, 1, 128, 32), (1, 1, 256, 40), (2, 2, 16, 300)])
-def test_delta_rule_kernel_over_spans_and_slots(H, G, d, e):
+def test_delta_rule_kernel_over_spans_and_slots(H, G, d, e, blocked):
     """Three requests in one launch: one from its first token, one that continues from a state another launch left (in
     a slot that a finished request used before), one single token; the state lies behind other floats of its slot."""
     torch.manual_seed(d + e)
@@ -143,7 +144,10 @@ def test_delta_rule_kernel_over_spans_and_slots(H, G, d, e):
     for r, n in lens.items():
         q = torch.nn.functional.normalize(mk(n, G * d).view(n, G, d), dim=-1) * d ** -0.5
         k = torch.nn.functional.normalize(mk(n, G * d).view(n, G, d), dim=-1)
-        data[r] = dict(q=q, k=k, v=mk(n, H * e).view(n, H, e), g=torch.rand(n, H, d) * 0.5 + 0.5, b=mk(n, H + 3))
+        g = torch.rand(n, H, d) * 0.5 + 0.5
+        g[n // 2] = 1e-30                          # a token that forgets nearly everything, in every channel
+        g[:, :, 0] = 1.0                           # a channel that never decays
+        data[r] = dict(q=q, k=k, v=mk(n, H * e).view(n, H, e), g=g, b=mk(n, H + 3))
     want = {}
     for r, n in lens.items():
         x = {k_: v_.double() for k_, v_ in data[r].items()}
@@ -159,8 +163,8 @@ def test_delta_rule_kernel_over_spans_and_slots(H, G, d, e):
         T = sum(b - a for _, _, a, b in parts)
         o = torch.empty(T, H * e, device=DEV)
         bsrc = cat("b")
-        ops.delta_rule(cat("q").view(T, -1), cat("k").view(T, -1), cat("v").view(T, -1), cat("g").view(T, -1),
-                       bsrc[:, 1:1 + H], spans_of(parts), H, G, d, e, state, off, o)
+        ops.delta_rule(cat("q").view(T, -1), cat("k").view(T, -1), cat("v").view(T, -1), torch.log(cat("g")).view(T, -1),
+                       bsrc[:, 1:1 + H], spans_of(parts), H, G, d, e, state, off, o, blocked=blocked)
         at = 0
         for r, _, a, b in parts:
             got[(r, a, b)] = o[at:at + b - a].cpu()
@@ -183,11 +187,11 @@ def test_second_half_of_a_low_rank_pair(dtype):
     bias, rate = torch.randn(H * per), torch.rand(H) + 0.5
     z = x.double()[:, off:off + R] @ w.double().T
     for mode, want, out_dtype in ((None, z, dtype), ("sigmoid", torch.sigmoid(z + bias.double()), "float32"),
-                                  ("decay", torch.exp(-rate.double().repeat_interleave(per) *
-                                                      torch.nn.functional.softplus(z + bias.double())), "float32")):
+                                  ("log_decay", -rate.double().repeat_interleave(per) *
+                                   torch.nn.functional.softplus(z + bias.double()), "float32")):
         out = torch.empty(T, H * per, device=DEV, dtype=DT[out_dtype])
         ops.low_rank_up(dev(x), off, dev(w), out, bias=None if mode is None else dev(bias), mode=mode,
-                        rate=dev(rate) if mode == "decay" else None)
+                        rate=dev(rate) if mode == "log_decay" else None)
         close(out, want, out_dtype, f"low rank, mode {mode}", rel=None if out_dtype == "float32" else 8e-3)
 
 
