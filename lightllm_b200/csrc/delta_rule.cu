@@ -21,6 +21,10 @@ namespace {
 
 constexpr int DELTA_STAGE = 16;
 
+// Floats of padding behind the `nr` rows that one of a column's `dg` threads owns in a staged row: it keeps the 16-byte
+// reads of the dg threads on different banks (rows of 4 lie side by side without any).
+__host__ __device__ constexpr int delta_pad(int nr, int dg) { return (dg > 1 && nr > 4) ? 4 : 0; }
+
 struct DeltaParams {
     const float* q;            // [T, G, dim]
     const float* k;            // [T, G, dim]
@@ -46,7 +50,7 @@ struct DeltaParams {
 template <int NR, int DG>
 __global__ void __launch_bounds__(256) delta_rule_kernel(DeltaParams p) {
     extern __shared__ __align__(16) float sm[];
-    constexpr int PADF = DG > 1 ? 4 : 0;                 // keeps the DG threads of a column on different banks
+    constexpr int PADF = delta_pad(NR, DG);
     constexpr int DPAD = DG * (NR + PADF);
     const int span = blockIdx.x, h = blockIdx.y;
     const int dim = p.dim, vdim = p.vdim;
@@ -178,14 +182,14 @@ __global__ void __launch_bounds__(256) delta_blocks_prepare_kernel(DeltaParams p
     float* kr = sm;                              // [C][RS]    k_t
     float* qr = kr + C * RS;                     // [C][RS]    q_t
     float* Ls = qr + C * RS;                     // [C][RS]    log decays, then their running sums L_t
-    const int nr = p.nr, padded = p.nr + (p.dg > 1 ? 4 : 0), dpad = p.dg * padded;
+    const int nr = p.nr, padded = p.nr + delta_pad(p.nr, p.dg), dpad = p.dg * padded;
     float* dst = p.scratch + ((size_t)blockIdx.x * p.H + h) * delta_block_floats(dpad);
     float* Qb = dst;                             // [C][dpad]  e^{L_t} q_t
     float* Kb = Qb + C * dpad;                   // [C][dpad]  e^{L_t} k_t
     float* Kp = Kb + C * dpad;                   // [C][dpad]  e^{L_n - L_t} k_t
     float* GC = Kp + C * dpad;                   // [dpad]     e^{L_n}
-    float* As = GC + dpad;                       // [C][C]     A_ts (s < t), else 0
-    float* Ms = As + C * C;                      // [C][C]     M_ts (s <= t), else 0
+    float* As = GC + dpad;                       // [C][C]     A_ts at [s][t] (s < t), else 0: a row holds what u_s adds to
+    float* Ms = As + C * C;                      // [C][C]     M_ts at [s][t] (s <= t), else 0    the tokens after it
     for (int it = threadIdx.x; it < C * dim; it += blockDim.x) {
         const int tl = it / dim, d = it - tl * dim;
         const size_t row = (size_t)(row0 + tl);
@@ -221,7 +225,7 @@ __global__ void __launch_bounds__(256) delta_blocks_prepare_kernel(DeltaParams p
         }
     }
     for (int pr = threadIdx.x; pr < C * C; pr += blockDim.x) {
-        const int t = pr / C, s = pr - t * C;
+        const int s = pr / C, t = pr - s * C;
         if (s > t) As[pr] = Ms[pr] = 0.0f;
     }
     for (int pr = threadIdx.x; pr < DELTA_PAIRS; pr += blockDim.x) {          // the pairs s <= t, packed: no idle lanes
@@ -237,8 +241,8 @@ __global__ void __launch_bounds__(256) delta_blocks_prepare_kernel(DeltaParams p
                 m = fmaf(qr[t * RS + d], w, m);
             }
         }
-        As[t * C + s] = s < t ? a : 0.0f;
-        Ms[t * C + s] = m;
+        As[s * C + t] = s < t ? a : 0.0f;
+        Ms[s * C + t] = m;
     }
 }
 
@@ -246,7 +250,7 @@ template <int NR, int DG>
 __global__ void __launch_bounds__(64) delta_rule_blocked_kernel(DeltaParams p) {
     extern __shared__ __align__(16) float sm[];
     constexpr int C = DELTA_STAGE;
-    constexpr int PADF = DG > 1 ? 4 : 0;
+    constexpr int PADF = delta_pad(NR, DG);
     constexpr int DPAD = DG * (NR + PADF);
     const int span = blockIdx.x, h = blockIdx.y;
     const int dim = p.dim, vdim = p.vdim;
@@ -286,12 +290,10 @@ __global__ void __launch_bounds__(64) delta_rule_blocked_kernel(DeltaParams p) {
             const int ee = blockIdx.z * p.EV + cc;
             vnext[i] = (it < C * p.EV && tl < n && ee < vdim) ? p.v[((size_t)(row0 + c0 + tl) * p.H + h) * vdim + ee] : 0.0f;
         }
-        bnext = 0.0f;
+        bnext = -INFINITY;          // (its sigmoid is 0; taken when the value is stored, not while the load is in flight)
         if (threadIdx.x < n) {
             const size_t at_b = (size_t)(row0 + c0 + threadIdx.x) * p.beta_stride + h;
-            const float z = p.beta_dtype == LLB_F32 ? ((const float*)p.beta)[at_b]
-                                                    : __bfloat162float(((const __nv_bfloat16*)p.beta)[at_b]);
-            bnext = 1.0f / (1.0f + expf(-z));
+            bnext = p.beta_dtype == LLB_F32 ? ((const float*)p.beta)[at_b] : __bfloat162float(((const __nv_bfloat16*)p.beta)[at_b]);
         }
     };
     auto store_vb = [&](int stage) {
@@ -301,7 +303,7 @@ __global__ void __launch_bounds__(64) delta_rule_blocked_kernel(DeltaParams p) {
             const int it = threadIdx.x + i * blockDim.x;
             if (it < C * p.EV) vsn[it] = vnext[i];
         }
-        if (threadIdx.x < C) vsn[C * p.EV + threadIdx.x] = bnext;
+        if (threadIdx.x < C) vsn[C * p.EV + threadIdx.x] = 1.0f / (1.0f + expf(-bnext));
     };
     fetch(first_block, 0);
     load_vb(0);
@@ -352,22 +354,29 @@ __global__ void __launch_bounds__(64) delta_rule_blocked_kernel(DeltaParams p) {
             }
             w[t] = (el < p.EV ? vs[t * p.EV + el] : 0.0f) - w[t];
         }
-        // forward substitution (every lane of a column computes the same u), and the read-out's part from inside the block
+        // forward substitution (every lane of a column computes the same u) and the read-out's part from inside the block,
+        // token s at a time: once u_s is known it is taken off every later token's right side and added to every later
+        // token's output, which are independent of one another (a token's sums still run over s in rising order)
         float u[C];
 #pragma unroll
-        for (int t = 0; t < C; ++t) {
-            float acc = w[t];
+        for (int s = 0; s < C; ++s) {
+            u[s] = bs[s] * w[s];
 #pragma unroll
-            for (int s = 0; s < t; ++s) acc = fmaf(-As[t * C + s], u[s], acc);
-            u[t] = bs[t] * acc;
+            for (int t4 = (s / 4) * 4; t4 < C; t4 += 4) {
+                const float4 a4 = *reinterpret_cast<const float4*>(As + s * C + t4);
+                const float4 m4 = *reinterpret_cast<const float4*>(Ms + s * C + t4);
+                const float av[4] = {a4.x, a4.y, a4.z, a4.w}, mv[4] = {m4.x, m4.y, m4.z, m4.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int t = t4 + i;
+                    if (t > s) w[t] = fmaf(-av[i], u[s], w[t]);
+                    if (t >= s) o[t] = fmaf(mv[i], u[s], o[t]);
+                }
+            }
         }
 #pragma unroll
-        for (int t = 0; t < C; ++t) {
-            float acc = o[t];
-#pragma unroll
-            for (int s = 0; s <= t; ++s) acc = fmaf(Ms[t * C + s], u[s], acc);
-            if (live && dg == 0 && t < n) p.out[((size_t)(row0 + c0 + t) * p.H + h) * vdim + e] = acc;
-        }
+        for (int t = 0; t < C; ++t)
+            if (live && dg == 0 && t < n) p.out[((size_t)(row0 + c0 + t) * p.H + h) * vdim + e] = o[t];
         // the state after the block
         {
             const float4* g4p = reinterpret_cast<const float4*>(GC + dg * (NR + PADF));
@@ -404,7 +413,7 @@ int launch_delta(const DeltaParams& p0, int num_spans, cudaStream_t stream) {
     DeltaParams p = p0;
     const int cols = 256 / DG;
     p.EV = p.vdim < cols ? p.vdim : cols;
-    constexpr int PADF = DG > 1 ? 4 : 0;
+    constexpr int PADF = delta_pad(NR, DG);
     const size_t smem = (size_t)(3 * DELTA_STAGE * DG * (NR + PADF) + DELTA_STAGE * p.EV + DELTA_STAGE) * sizeof(float);
     const int threads = ((p.EV * DG + 31) / 32) * 32;
     const dim3 grid(num_spans, p.H, (p.vdim + p.EV - 1) / p.EV);
@@ -543,10 +552,10 @@ LLB_EXPORT int llb_delta_rule(const float* q, const float* k, const float* v, co
     LLB_REQUIRE(!blocked || (scratch && max_blocks > 0), "delta_rule: the blocked walk needs scratch");
     if (blocked) {          // more threads a column: what paces a block of tokens is a warp's own instruction chain
         if (dim <= 16) return launch_delta<4, 4>(p, num_spans, stream);
-        if (dim <= 32) return launch_delta<8, 4>(p, num_spans, stream);
-        if (dim <= 64) return launch_delta<8, 8>(p, num_spans, stream);
-        if (dim <= 128) return launch_delta<16, 8>(p, num_spans, stream);
-        return launch_delta<32, 8>(p, num_spans, stream);
+        if (dim <= 32) return launch_delta<4, 8>(p, num_spans, stream);
+        if (dim <= 64) return launch_delta<4, 16>(p, num_spans, stream);
+        if (dim <= 128) return launch_delta<8, 16>(p, num_spans, stream);
+        return launch_delta<16, 16>(p, num_spans, stream);
     }
     if (dim <= 16) return launch_delta<16, 1>(p, num_spans, stream);
     if (dim <= 32) return launch_delta<16, 2>(p, num_spans, stream);
@@ -556,9 +565,9 @@ LLB_EXPORT int llb_delta_rule(const float* q, const float* k, const float* v, co
 }
 
 LLB_EXPORT long long llb_delta_rule_scratch_floats(int max_blocks, int H, int dim) {
-    const int nr = dim <= 16 ? 4 : dim <= 64 ? 8 : dim <= 128 ? 16 : 32;          // as llb_delta_rule picks them
-    const int dg = dim <= 32 ? 4 : 8;
-    return (long long)max_blocks * H * delta_block_floats(dg * (nr + 4));
+    const int nr = dim <= 64 ? 4 : dim <= 128 ? 8 : 16;          // as llb_delta_rule picks them
+    const int dg = dim <= 16 ? 4 : dim <= 32 ? 8 : 16;
+    return (long long)max_blocks * H * delta_block_floats(dg * (nr + delta_pad(nr, dg)));
 }
 
 // out[t, n] = f(sum_r x[t, x_off + r] * w[n, r] + bias[n]) for T rows of x (row stride x_stride elements, float or bf16),

@@ -1,6 +1,7 @@
 """Feed-forward layers made of routed experts."""
 from __future__ import annotations
 
+import os
 from typing import Dict, List, Optional
 
 import torch
@@ -101,10 +102,14 @@ class RoutedExperts(FeedForward):
 
     def grouped_pays(self, rows: int) -> bool:
         """Whether the grouped contractions need less arithmetic than every expert on every row: ``rows * top`` pairs plus
-        half a tile of padding an expert, against ``rows * experts``."""
-        return (self.GROUPED and self.w_down_rows is not None and ops.has_tcgen05()
-                and rows * self.top + 64 * self.num_experts < rows * self.num_experts
-                and rows * self.top + 128 * self.num_experts > 128)
+        half a tile of padding an expert, against ``rows * experts``.  ``LLB_MOE_GROUPED=always|never`` in the environment
+        overrides the rule (for comparisons)."""
+        if not (self.GROUPED and self.w_down_rows is not None and ops.has_tcgen05()):
+            return False
+        forced = os.environ.get("LLB_MOE_GROUPED", "")
+        if forced in ("always", "never"):
+            return forced == "always"
+        return rows * self.top + 64 * self.num_experts < rows * self.num_experts
 
     def _forward_grouped(self, x, residual) -> None:
         T, E, I, D = x.shape[0], self.num_experts, self.intermediate_size, self.hidden_size
