@@ -486,7 +486,8 @@ __global__ void __launch_bounds__(256) low_rank_up_kernel(LowRankParams p, int T
     float acc[LR_ROWS];
 #pragma unroll
     for (int tl = 0; tl < LR_ROWS; ++tl) acc[tl] = 0.0f;
-    for (int r = 0; r < R4; r += 4) {
+#pragma unroll 4
+    for (int r = 0; r < R4; r += 4) {          // (unrolled: the weights of four steps are asked for before the first is used)
         float w4[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) w4[j] = r + j < p.R ? llb_to_float(wr[r + j]) : 0.0f;

@@ -28,7 +28,32 @@ int launch_cast(const void* src, void* dst, long long n, int accumulate, cudaStr
     return llb_check_launch("cast_add");
 }
 
+// out[t, 0:D] = a[t, :] (float, converted), out[t, D:2D] = b[t, :] (already in out's dtype)
+template <typename TO>
+__global__ void cast_concat_kernel(const float* __restrict__ a, const TO* __restrict__ b, TO* __restrict__ out, long long T, int D) {
+    const long long n = T * D, stride = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const long long t = i / D;
+        const int d = (int)(i - t * D);
+        out[t * 2 * D + d] = llb_from_float<TO>(a[i]);
+        out[t * 2 * D + D + d] = b[i];
+    }
+}
+
 }  // namespace
+
+// out [T, 2D] = [a | b] row by row: a float [T, D] converted to out's dtype, b [T, D] in out's dtype.
+LLB_EXPORT int llb_cast_concat(const float* a, const void* b, void* out, int dtype, long long T, int D, cudaStream_t stream) {
+    if (T == 0) return 0;
+    LLB_REQUIRE(T > 0 && D > 0 && a && b && out, "cast_concat: bad arguments");
+    const long long n = T * D;
+    const int blocks = (int)((n + 255) / 256 < 1184 ? (n + 255) / 256 : 1184);
+    if (dtype == LLB_F32) cast_concat_kernel<float><<<blocks, 256, 0, stream>>>(a, (const float*)b, (float*)out, T, D);
+    else if (dtype == LLB_BF16)
+        cast_concat_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(a, (const __nv_bfloat16*)b, (__nv_bfloat16*)out, T, D);
+    else return llb_fail("cast_concat: unknown dtype %d", dtype);
+    return llb_check_launch("cast_concat");
+}
 
 // dst[i] = src[i] (accumulate == 0) or dst[i] + src[i], for n elements; each side float or bf16.
 LLB_EXPORT int llb_cast_add(const void* src, int src_dtype, void* dst, int dst_dtype, long long n, int accumulate,

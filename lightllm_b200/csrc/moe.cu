@@ -2,7 +2,7 @@
 // `top` experts with the largest choice scores (score + an optional per-expert correction that takes part in the choice
 // only), weights = the chosen experts' scores (optionally renormalised to sum 1) times `scale`.
 //
-// One warp per token.  The result is written twice: as lists (`ids`, `weights` [T, top], in the order of the choice) and
+// One block per token, a warp an expert's dot product.  The result is written twice: as lists (`ids`, `weights` [T, top], in the order of the choice) and
 // as a dense row of weights over all experts (`dense` [T, E], zero for the experts not chosen), which is what the
 // contraction-shaped expert path multiplies the experts' activations by.
 #include "common.cuh"
@@ -12,25 +12,41 @@ namespace {
 constexpr int MOE_MAX_EXPERTS = 512;
 
 template <typename TX>
-__global__ void __launch_bounds__(128) moe_route_kernel(const TX* __restrict__ x, const float* __restrict__ w,
+__global__ void __launch_bounds__(256) moe_route_kernel(const TX* __restrict__ x, const float* __restrict__ w,
                                                         const float* __restrict__ correction, int T, int D, int E, int top,
                                                         int softmax, int renorm, float scale, int* __restrict__ ids,
                                                         float* __restrict__ weights, float* __restrict__ dense) {
-    extern __shared__ float sm[];                // per warp: score [E], choice [E]
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
-    if (t >= T) return;
-    float* score = sm + (size_t)warp * 2 * E;
+    extern __shared__ __align__(16) float sm[];  // the token's row [D4], then score [E], choice [E]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    const int t = blockIdx.x;
+    const int D4 = (D + 3) & ~3;
+    float* xs = sm;
+    float* score = sm + D4;
     float* choice = score + E;
     const TX* xr = x + (size_t)t * D;
-    for (int e = 0; e < E; ++e) {
+    for (int d = threadIdx.x; d < D4; d += blockDim.x) xs[d] = d < D ? llb_to_float(xr[d]) : 0.0f;
+    __syncthreads();
+    // a warp an expert: the lanes' loads of a row are all in flight at once
+    const bool vec = D % 4 == 0 && (uintptr_t)w % 16 == 0;
+    for (int e = warp; e < E; e += nwarps) {
         const float* wr = w + (size_t)e * D;
-        float acc = 0.0f;
-        for (int d = lane; d < D; d += 32) acc = fmaf(llb_to_float(xr[d]), wr[d], acc);
-        acc = llb_warp_sum(acc);
+        float a0 = 0.0f, a1 = 0.0f;
+        if (vec) {
+#pragma unroll 4
+            for (int d = lane * 4; d < D; d += 128) {
+                const float4 w4 = *reinterpret_cast<const float4*>(wr + d);
+                const float4 x4 = *reinterpret_cast<const float4*>(xs + d);
+                a0 = fmaf(x4.x, w4.x, a0); a1 = fmaf(x4.y, w4.y, a1);
+                a0 = fmaf(x4.z, w4.z, a0); a1 = fmaf(x4.w, w4.w, a1);
+            }
+        } else {
+            for (int d = lane; d < D; d += 32) a0 = fmaf(xs[d], wr[d], a0);
+        }
+        const float acc = llb_warp_sum(a0 + a1);
         if (lane == 0) score[e] = acc;
     }
-    __syncwarp();
+    __syncthreads();
+    if (warp != 0) return;
     if (softmax) {
         float m = -INFINITY;
         for (int e = lane; e < E; e += 32) m = fmaxf(m, score[e]);
@@ -74,12 +90,10 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const TX* __restrict__ x
     }
     const float mul = renorm ? scale / total : scale;
     __syncwarp();
-    if (lane < top || top > 32) {
-        for (int k = lane; k < top; k += 32) {
-            const float wgt = weights[(size_t)t * top + k] * mul;
-            weights[(size_t)t * top + k] = wgt;
-            dense[(size_t)t * E + ids[(size_t)t * top + k]] = wgt;
-        }
+    for (int k = lane; k < top; k += 32) {
+        const float wgt = weights[(size_t)t * top + k] * mul;
+        weights[(size_t)t * top + k] = wgt;
+        dense[(size_t)t * E + ids[(size_t)t * top + k]] = wgt;
     }
 }
 
@@ -150,7 +164,108 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restric
     }
 }
 
+// Fewer (token, expert) pairs than experts (a decode step of a few rows): every pair streams its own expert's weights, and
+// the experts that nobody chose are not read at all.  One warp per output: 16-byte loads of the weight row against the
+// pair's input row in shared memory, float sums.
+constexpr int PAIR_OUTS = 32;          // outputs a block (8 warps, 4 each)
+
+// R neighbouring weight rows of K numbers against one input row in shared memory: every lane has R 16-byte loads in
+// flight per step along K, which is what lets a few blocks pull at the memory's bandwidth.
+template <int R>
+__device__ __forceinline__ void dot_rows_bf16(const __nv_bfloat16* __restrict__ w, const float* __restrict__ xs, int K, int lane,
+                                              float (&acc)[R]) {
+#pragma unroll
+    for (int r = 0; r < R; ++r) acc[r] = 0.0f;
+    for (int k = lane * 8; k < K; k += 256) {          // K is a multiple of 8
+        uint4 raw[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) raw[r] = *reinterpret_cast<const uint4*>(w + (size_t)r * K + k);
+        const float4 x0 = *reinterpret_cast<const float4*>(xs + k), x1 = *reinterpret_cast<const float4*>(xs + k + 4);
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[r]);
+            const float2 f0 = __bfloat1622float2(h[0]), f1 = __bfloat1622float2(h[1]);
+            const float2 f2 = __bfloat1622float2(h[2]), f3 = __bfloat1622float2(h[3]);
+            float a = acc[r];
+            a = fmaf(f0.x, x0.x, a); a = fmaf(f0.y, x0.y, a); a = fmaf(f1.x, x0.z, a); a = fmaf(f1.y, x0.w, a);
+            a = fmaf(f2.x, x1.x, a); a = fmaf(f2.y, x1.y, a); a = fmaf(f3.x, x1.z, a); a = fmaf(f3.y, x1.w, a);
+            acc[r] = a;
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) acc[r] = llb_warp_sum(acc[r]);
+}
+
+constexpr int PAIR_WARP_OUTS = PAIR_OUTS / 8;          // outputs a warp
+
+// act[pair, j] = silu(W_gate[e] x) * (W_up[e] x) with (gate_j, up_j) in rows 2j, 2j + 1 of expert e's block of w
+__global__ void __launch_bounds__(256) moe_pairs_gate_up_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                                                                const int* __restrict__ ids, int top, int D, int F,
+                                                                __nv_bfloat16* __restrict__ act) {
+    extern __shared__ __align__(16) float xs[];          // [D]
+    const int pair = blockIdx.y, e = ids[pair];
+    const __nv_bfloat16* xr = x + (size_t)(pair / top) * D;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) xs[d] = __bfloat162float(xr[d]);
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const __nv_bfloat16* we = w + (size_t)e * 2 * F * D;
+    const int j0 = blockIdx.x * PAIR_OUTS + warp * PAIR_WARP_OUTS;
+    if (j0 + PAIR_WARP_OUTS <= F) {
+        float acc[2 * PAIR_WARP_OUTS];
+        dot_rows_bf16<2 * PAIR_WARP_OUTS>(we + (size_t)(2 * j0) * D, xs, D, lane, acc);
+        if (lane == 0)
+            for (int i = 0; i < PAIR_WARP_OUTS; ++i)
+                act[(size_t)pair * F + j0 + i] = __float2bfloat16_rn(llb_silu(acc[2 * i]) * acc[2 * i + 1]);
+    } else {
+        for (int j = j0; j < F; ++j) {
+            float acc[2];
+            dot_rows_bf16<2>(we + (size_t)(2 * j) * D, xs, D, lane, acc);
+            if (lane == 0) act[(size_t)pair * F + j] = __float2bfloat16_rn(llb_silu(acc[0]) * acc[1]);
+        }
+    }
+}
+
+// y[pair, d] = W_down[e][d, :] . act[pair, :] with expert e's down matrix in rows e * D .. of w
+__global__ void __launch_bounds__(256) moe_pairs_down_kernel(const __nv_bfloat16* __restrict__ act, const __nv_bfloat16* __restrict__ w,
+                                                             const int* __restrict__ ids, int D, int F, float* __restrict__ y) {
+    extern __shared__ __align__(16) float as[];          // [F]
+    const int pair = blockIdx.y, e = ids[pair];
+    for (int f = threadIdx.x; f < F; f += blockDim.x) as[f] = __bfloat162float(act[(size_t)pair * F + f]);
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const __nv_bfloat16* we = w + (size_t)e * D * F;
+    const int d0 = blockIdx.x * PAIR_OUTS + warp * PAIR_WARP_OUTS;
+    if (d0 + PAIR_WARP_OUTS <= D) {
+        float acc[PAIR_WARP_OUTS];
+        dot_rows_bf16<PAIR_WARP_OUTS>(we + (size_t)d0 * F, as, F, lane, acc);
+        if (lane == 0)
+            for (int i = 0; i < PAIR_WARP_OUTS; ++i) y[(size_t)pair * D + d0 + i] = acc[i];
+    } else {
+        for (int d = d0; d < D; ++d) {
+            float acc[1];
+            dot_rows_bf16<1>(we + (size_t)d * F, as, F, lane, acc);
+            if (lane == 0) y[(size_t)pair * D + d] = acc[0];
+        }
+    }
+}
+
 }  // namespace
+
+// The experts of a few pairs, read pair by pair (bfloat16; D and F multiples of 8): x [T, D]; ids int [T * top]; w_gate_up
+// [E * 2F, D] with (gate_j, up_j) in neighbouring rows; w_down [E * D, F]; act [T * top, F] scratch; y float [T * top, D].
+LLB_EXPORT int llb_moe_pairs(const void* x, const int* ids, int pairs, int top, int D, int F, const void* w_gate_up,
+                             const void* w_down, void* act, float* y, cudaStream_t stream) {
+    if (pairs == 0) return 0;
+    LLB_REQUIRE(pairs > 0 && top > 0 && x && ids && w_gate_up && w_down && act && y, "moe_pairs: bad arguments");
+    LLB_REQUIRE(D > 0 && F > 0 && D % 8 == 0 && F % 8 == 0 && D <= 12288 && F <= 12288, "moe_pairs: D=%d, F=%d must be multiples of 8", D, F);
+    moe_pairs_gate_up_kernel<<<dim3((F + PAIR_OUTS - 1) / PAIR_OUTS, pairs), 256, D * sizeof(float), stream>>>(
+        (const __nv_bfloat16*)x, (const __nv_bfloat16*)w_gate_up, ids, top, D, F, (__nv_bfloat16*)act);
+    int rc = llb_check_launch("moe_pairs_gate_up");
+    if (rc) return rc;
+    moe_pairs_down_kernel<<<dim3((D + PAIR_OUTS - 1) / PAIR_OUTS, pairs), 256, F * sizeof(float), stream>>>(
+        (const __nv_bfloat16*)act, (const __nv_bfloat16*)w_down, ids, D, F, y);
+    return llb_check_launch("moe_pairs_down");
+}
 
 // ids int [T * top] -> slot int [T * top], tile_group int [max_tiles] (see moe_sort_kernel); max_tiles >= T * top / align + E.
 LLB_EXPORT int llb_moe_sort(const int* ids, int pairs, int E, int align, int max_tiles, int* slot, int* tile_group,
@@ -193,9 +308,11 @@ LLB_EXPORT int llb_moe_route(const void* x, int x_dtype, const float* w, const f
     LLB_REQUIRE(T > 0 && D > 0 && x && w && ids && weights && dense, "moe_route: bad arguments");
     LLB_REQUIRE(E > 0 && E <= MOE_MAX_EXPERTS && top > 0 && top <= E, "moe_route: top %d of %d experts (at most %d)", top, E,
                 MOE_MAX_EXPERTS);
-    const int warps = 4;
-    const size_t smem = (size_t)warps * 2 * E * sizeof(float);
-    const unsigned blocks = (unsigned)((T + warps - 1) / warps);
+    // a block a token; as many warps as there are experts to walk side by side, at most eight
+    const int warps = E < 8 ? (E < 1 ? 1 : E) : 8;
+    const size_t smem = (size_t)(((D + 3) & ~3) + 2 * E) * sizeof(float);
+    LLB_REQUIRE(smem <= 48 * 1024, "moe_route: rows of %d numbers do not fit in shared memory", D);
+    const unsigned blocks = (unsigned)T;
     if (x_dtype == LLB_F32)
         moe_route_kernel<float><<<blocks, warps * 32, smem, stream>>>((const float*)x, w, correction, T, D, E, top, softmax,
                                                                       renorm, scale, ids, weights, dense);

@@ -426,14 +426,23 @@ def _state_base(state: torch.Tensor):
     return state.data_ptr(), state.numel() // state.shape[0]
 
 
+def cast_concat(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> None:
+    """out [T, 2D] = [a | b]: a float32 [T, D] converted to out's dtype, b [T, D] already in it."""
+    T, D = a.shape
+    if a.dtype != torch.float32 or tuple(b.shape) != (T, D) or b.dtype != out.dtype or tuple(out.shape) != (T, 2 * D):
+        raise KernelError("cast_concat: sizes or dtypes do not fit")
+    _check(lib().llb_cast_concat(_ptr(a), _ptr(b), _ptr(out), _dt(out), ctypes.c_longlong(T), D, _stream()))
+
+
 def conv_prepare(src: torch.Tensor, c0: int, channels: int, weight: torch.Tensor, segments, ctx_spans, state,
                  tail_off: int, slot_mapping: Optional[torch.Tensor] = None, freq: Optional[torch.Tensor] = None,
-                 rot_scale: float = 1.0) -> None:
+                 rot_scale: float = 1.0, fuse_tail: bool = False) -> None:
     """Short causal convolution (``weight`` float32 [channels, taps]) over columns ``c0 .. c0+channels`` of ``src`` [T, C],
     then per segment activation, rotation of pairs (2i, 2i+1) by ``positions * freq[i]`` (cos and sin times
     ``rot_scale``), head norm and scale.  ``ctx_spans = (span_row, span_len, span_pos, span_slot, num_spans)``;
     ``state`` float32 [slots, ...] holds each request's last ``taps - 1`` inputs at ``tail_off`` floats into its slot
-    (``None`` when ``taps == 1``)."""
+    (``None`` when ``taps == 1``).  ``fuse_tail`` (a step whose spans are all single tokens): the new tails are written by
+    this launch and :func:`conv_tail_update` is not needed."""
     T, C = src.shape
     taps = weight.shape[1]
     if weight.dtype != torch.float32 or weight.shape[0] != channels or c0 + channels > C:
@@ -458,7 +467,8 @@ def conv_prepare(src: torch.Tensor, c0: int, channels: int, weight: torch.Tensor
         I(*[s.head_dim for s in segments]), I(*[{None: 0, "silu": 1}[s.act] for s in segments]),
         I(*[s.rotary_dim for s in segments]), I(*[CONV_NORMS[s.norm] for s in segments]),
         Fl(*[s.eps for s in segments]), Fl(*[s.scale for s in segments]), P(*[s.out.data_ptr() for s in segments]),
-        I(*[_dt(s.out) for s in segments]), I(*[1 if s.to_cache else 0 for s in segments]), _stream()))
+        I(*[_dt(s.out) for s in segments]), I(*[1 if s.to_cache else 0 for s in segments]), 1 if fuse_tail else 0,
+        _stream()))
 
 
 def conv_tail_update(src: torch.Tensor, c0: int, channels: int, taps: int, ctx_spans, state: torch.Tensor,
@@ -584,6 +594,22 @@ def moe_combine(y: torch.Tensor, slot: torch.Tensor, weights: torch.Tensor, resi
         raise KernelError("moe_combine: sizes do not fit")
     _check(lib().llb_moe_combine(_f32(y, "y"), _i32(slot, "slot"), _f32(weights, "weights"), T, top, D, _f32(residual, "residual"),
                                  _stream()))
+
+
+def moe_pairs(x: torch.Tensor, ids: torch.Tensor, w_gate_up: torch.Tensor, w_down_rows: torch.Tensor, act: torch.Tensor,
+              y: torch.Tensor) -> None:
+    """The chosen experts of a few rows, pair by pair (bfloat16): ``y[t*top + k] = W_down[e] (silu(W_gate[e] x_t) *
+    (W_up[e] x_t))`` with e = ids[t, k]; ``w_gate_up`` [E*2F, D] (gate and up rows interleaved), ``w_down_rows`` [E*D, F];
+    ``act`` bfloat16 [T*top, F] scratch; ``y`` float32 [T*top, D]."""
+    T, D = x.shape
+    pairs, top = ids.numel(), ids.shape[1]
+    F = w_down_rows.shape[1]
+    if x.dtype != torch.bfloat16 or w_gate_up.dtype != torch.bfloat16 or w_down_rows.dtype != torch.bfloat16 or \
+            w_gate_up.shape[1] != D or tuple(act.shape) != (pairs, F) or act.dtype != torch.bfloat16 or \
+            tuple(y.shape) != (pairs, D) or y.dtype != torch.float32 or pairs != T * top:
+        raise KernelError("moe_pairs: sizes or dtypes do not fit")
+    _check(lib().llb_moe_pairs(_ptr(x), _i32(ids, "ids"), pairs, top, D, F, _ptr(w_gate_up), _ptr(w_down_rows), _ptr(act),
+                               _f32(y, "y"), _stream()))
 
 
 def gemm_tcgen05_grouped(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int, groups: int,

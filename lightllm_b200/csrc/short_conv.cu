@@ -11,6 +11,8 @@
 // a span's first token come from the request's state slot (`tail`: [taps - 1, C] floats, the last projected values of
 // the request, oldest first); positions before 0 are zeros whatever the slot holds, so a slot that another request
 // used needs no clearing.  `llb_conv_tail_update` then writes the new tail; it runs after every reader of the old one.
+// In a step whose spans are all single tokens exactly one warp reads a (request, head)'s channels of the tail, so that
+// warp writes their new tail itself (`fuse_tail`) and the second launch is saved.
 //
 // One warp per (token, head): a lane holds pairs of neighbouring dimensions, so rotation needs no exchange and the norm
 // one warp sum.  All arithmetic is float; inputs and outputs float or bf16.
@@ -51,6 +53,7 @@ struct ConvParams {
     int total_heads;
     ConvSegment seg[CONV_SEGMENTS];
     int num_segments;
+    int fuse_tail;               // every span is one token: the warp that read a head's tail writes the new one
 };
 
 __device__ __forceinline__ int span_of_row(const int* span_row, int num_spans, int row) {
@@ -117,6 +120,23 @@ __global__ void __launch_bounds__(128) conv_prepare_kernel(ConvParams p) {
         ss = llb_warp_sum(ss);
         mul *= 1.0f / sqrtf((sg.norm == 1 ? ss / (float)hd : ss) + sg.eps);
     }
+    if (p.fuse_tail && taps > 1) {          // (local == 0: the span is this one token)
+        float* wtail = p.state + (long long)p.span_slot[span] * p.state_stride + p.tail_off;
+#pragma unroll
+        for (int i = 0; i < CONV_MAX_PAIRS; ++i) {
+            const int d = 2 * (lane + 32 * i);
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                if (d + e >= hd) continue;
+                const int c = cbase + d + e;
+                float keep[CONV_MAX_TAPS];
+                for (int j = 0; j + 1 < taps; ++j)          // positions pos - (taps - 2) + j: the old tail's j + 1, the token itself last
+                    keep[j] = j + 2 == taps ? llb_to_float(src[(size_t)t * p.row_stride + p.c0 + c])
+                                            : (pos - (taps - 2) + j >= 0 ? wtail[(size_t)(j + 1) * p.C + c] : 0.0f);
+                for (int j = 0; j + 1 < taps; ++j) wtail[(size_t)j * p.C + c] = keep[j];
+            }
+        }
+    }
     size_t orow;
     if (sg.to_cache) {
         const int slot = p.slot_mapping[t];
@@ -175,6 +195,7 @@ __global__ void __launch_bounds__(256) conv_tail_kernel(ConvParams p) {
 // parallel arrays of `num_segments` entries: first channel, heads, head size, activation (0 none, 1 SiLU), rotary_dim (0
 // none; pairs (2i, 2i+1) by freq [rotary_dim / 2] and rot_scale), norm (0 none, 1 unit root mean square, 2 unit length)
 // with eps, post_scale, output pointer with dtype, and whether the output is the cache (rows by slot_mapping [T]).
+// fuse_tail != 0 (only when every span is one token): the new tails are written here and llb_conv_tail_update is not needed.
 LLB_EXPORT int llb_conv_prepare(const void* src, int src_dtype, long long row_stride, int c0, int C, int taps, int T,
                                 const float* w, const int* span_row, const int* span_len, const int* span_pos,
                                 const int* span_slot, int num_spans, float* state, long long state_stride,
@@ -182,8 +203,9 @@ LLB_EXPORT int llb_conv_prepare(const void* src, int src_dtype, long long row_st
                                 int num_segments, const int* seg_col0, const int* seg_heads, const int* seg_hd,
                                 const int* seg_act, const int* seg_rotary, const int* seg_norm, const float* seg_eps,
                                 const float* seg_scale, void* const* seg_out, const int* seg_out_dtype,
-                                const int* seg_to_cache, cudaStream_t stream) {
+                                const int* seg_to_cache, int fuse_tail, cudaStream_t stream) {
     if (T == 0) return 0;
+    LLB_REQUIRE(!fuse_tail || T == num_spans, "conv_prepare: the tail is only written here when every span is one token");
     LLB_REQUIRE(T > 0 && C > 0 && src && w && span_row && span_len && span_pos && span_slot && num_spans > 0,
                 "conv_prepare: bad arguments");
     LLB_REQUIRE(taps >= 1 && taps <= CONV_MAX_TAPS, "conv_prepare: %d taps; at most %d", taps, CONV_MAX_TAPS);
@@ -193,7 +215,7 @@ LLB_EXPORT int llb_conv_prepare(const void* src, int src_dtype, long long row_st
     p.src = src; p.row_stride = row_stride; p.c0 = c0; p.C = C; p.taps = taps; p.T = T; p.num_spans = num_spans;
     p.w = w; p.span_row = span_row; p.span_len = span_len; p.span_pos = span_pos; p.span_slot = span_slot;
     p.state = state; p.state_stride = state_stride; p.tail_off = tail_off; p.slot_mapping = slot_mapping;
-    p.freq = freq; p.rot_scale = rot_scale; p.num_segments = num_segments; p.total_heads = 0;
+    p.freq = freq; p.rot_scale = rot_scale; p.num_segments = num_segments; p.total_heads = 0; p.fuse_tail = fuse_tail;
     for (int i = 0; i < num_segments; ++i) {
         ConvSegment& s = p.seg[i];
         s.col0 = seg_col0[i]; s.heads = seg_heads[i]; s.hd = seg_hd[i]; s.act = seg_act[i]; s.rotary_dim = seg_rotary[i];

@@ -108,8 +108,9 @@ class ConvAttentionMixer(AttentionMixer):
                     ops.ConvSegment((H + G) * hd, G, vd, cache.v, to_cache=True)]
         spans = span_arrays(ctx)
         ops.conv_prepare(fused, 0, self.channels, self.w_conv, segments, spans, cache.state, 0,
-                         ctx.slot_mapping[cache.group], freq, getattr(self.position, "magnitude", 1.0))
-        if self.conv_taps > 1:
+                         ctx.slot_mapping[cache.group], freq, getattr(self.position, "magnitude", 1.0),
+                         fuse_tail=ctx.decode_only)
+        if self.conv_taps > 1 and not ctx.decode_only:
             ops.conv_tail_update(fused, 0, self.channels, self.conv_taps, spans, cache.state, 0)
         attn = torch.empty((T, H * vd), dtype=x.dtype, device=x.device)
         self.attend(q, cache, ctx, attn)

@@ -101,8 +101,10 @@ class ChannelDeltaMixer(Mixer):
                     ops.ConvSegment(2 * G * hd, H, vd, v, act="silu")]
         spans = span_arrays(ctx)
         tail_off = self.state_floats
-        ops.conv_prepare(fused, 0, self.channels, self.w_conv, segments, spans, cache.state, tail_off)
-        ops.conv_tail_update(fused, 0, self.channels, self.conv_taps, spans, cache.state, tail_off)
+        ops.conv_prepare(fused, 0, self.channels, self.w_conv, segments, spans, cache.state, tail_off,
+                         fuse_tail=ctx.decode_only)
+        if not ctx.decode_only:
+            ops.conv_tail_update(fused, 0, self.channels, self.conv_taps, spans, cache.state, tail_off)
         c = self.channels
         decay = torch.empty((T, H * hd), **f32)
         ops.low_rank_up(fused, c + H, self.w_a2, decay, bias=self.dt_bias, mode="log_decay", rate=self.rate)

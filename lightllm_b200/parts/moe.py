@@ -22,7 +22,7 @@ class RoutedExperts(FeedForward):
     tensor that takes part in the choice only, or none), weights = the chosen experts' scores, divided by their sum
     with ``renormalize``, times ``route_scale``.
 
-    Two ways to run the experts, both with launches whose shapes follow from the step's token count alone, so that steps
+    Three ways to run the experts, all with launches whose shapes follow from the step's token count alone, so that steps
     replay from CUDA graphs:
 
     * **every expert on every row** (few rows, float32, odd sizes): gate and up of all experts are the rows of one matrix
@@ -30,6 +30,8 @@ class RoutedExperts(FeedForward):
       multiplied by w_e (zero for the experts a token did not choose) and the down matrices, side by side along the inner
       dimension, add the weighted sum into the stream: ``sum_e w_e W_down_e a_e = [W_down_0 .. W_down_E-1] [w_0 a_0; ..;
       w_E-1 a_E-1]``.  A decode step reads every expert's weights once, as it would anyway from about ``E / top`` rows on.
+    * **pair by pair** (bfloat16, fewer (token, expert) pairs than experts: a decode step of a few rows): every pair streams
+      its own expert's weights through a CUDA-core kernel and the experts nobody chose are not read.
     * **grouped** (bfloat16 on the tensor cores, from ``GROUPED_MIN_ROWS`` rows on or where it needs less arithmetic): the
       (token, expert) pairs are sorted by expert on the device, every expert's rows padded to whole tiles of 128, the rows
       gathered, and two grouped contractions (each row tile takes its expert's weights) make the experts' outputs in
@@ -93,6 +95,7 @@ class RoutedExperts(FeedForward):
         self.w_down = torch.cat([w.to(wdt) for w in downs], dim=1).contiguous()          # [D, E * I]
         if wdt == torch.bfloat16 and dtype == torch.bfloat16 and self.top < E and D % 8 == 0 and I % 8 == 0:
             self.w_down_rows = torch.cat(downs, dim=0).contiguous()                     # [E * D, I]: expert by expert
+            self._iota = torch.arange(E, dtype=torch.int32, device=device)              # each pair's own row, pair by pair
         L.reserve_fused_scratch(device, E * 2 * I)
 
     def route(self, x):
@@ -116,6 +119,15 @@ class RoutedExperts(FeedForward):
             return forced == "always"
         return rows >= self.GROUPED_MIN_ROWS or rows * self.top + 64 * self.num_experts < rows * self.num_experts
 
+    def _forward_pairs(self, x, residual) -> None:
+        T = x.shape[0]
+        ids, weights, _ = self.route(x)
+        pairs = T * self.top
+        act = torch.empty((pairs, self.intermediate_size), dtype=x.dtype, device=x.device)
+        y = torch.empty((pairs, self.hidden_size), dtype=torch.float32, device=x.device)
+        ops.moe_pairs(x, ids, self.w_gate_up, self.w_down_rows, act, y)
+        ops.moe_combine(y, self._iota[:pairs], weights, residual)
+
     def _forward_grouped(self, x, residual) -> None:
         T, E, I, D = x.shape[0], self.num_experts, self.intermediate_size, self.hidden_size
         ids, weights, _ = self.route(x)
@@ -135,6 +147,10 @@ class RoutedExperts(FeedForward):
     def forward(self, x, residual, ctx=None) -> None:
         if isinstance(x, LazyNorm):
             x = x.materialize()
+        if x.dtype == torch.bfloat16 and self.w_down_rows is not None and self.GROUPED and \
+                x.shape[0] * self.top < self.num_experts and os.environ.get("LLB_MOE_GROUPED", "") != "never":
+            self._forward_pairs(x, residual)
+            return
         if x.dtype == torch.bfloat16 and self.grouped_pays(x.shape[0]):
             self._forward_grouped(x, residual)
             return

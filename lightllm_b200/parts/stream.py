@@ -18,9 +18,9 @@ class StreamReinjection(Part):
     part, ``keep_output=True``) and a learned vector is added, e.g. before every pass of a looped stretch of layers.
 
     ``weight_name`` is ``[hidden, 2 * hidden]`` with the stream's columns first; ``step_name`` is ``[rows, hidden]`` and
-    ``index`` picks the row.  Parts of several run entries may name the same tensors (one per pass).  The two halves of
-    the contraction run as two contractions that add into the cleared float stream, the step vector as the first one's
-    bias, so the new stream is never rounded to the compute dtype."""
+    ``index`` picks the row.  Parts of several run entries may name the same tensors (one per pass).  One kernel lays
+    ``[h | e]`` side by side in the compute dtype, one contraction with the step vector as its bias writes the new float
+    stream, which is never rounded to the compute dtype."""
 
     role = "stream"
     graph_safe = True
@@ -31,28 +31,24 @@ class StreamReinjection(Part):
         join = lambda tail: f"{prefix}.{tail}" if prefix else tail
         self.weight_name, self.step_name = join(weight_name), join(step_name)
         self.hidden_size, self.steps, self.index = hidden_size, steps, index
-        self.w_stream = self.w_embedding = self.step = None
+        self.weight = self.step = None
 
     def weight_specs(self) -> List[WeightSpec]:
         D = self.hidden_size
         return [WeightSpec(self.weight_name, (D, 2 * D)), WeightSpec(self.step_name, (self.steps, D), init=("normal", 0.1))]
 
     def bind(self, tensors, dtype, device) -> None:
-        w = tensors[self.weight_name]
-        D = self.hidden_size
-        self.w_stream = w[:, :D].contiguous()
-        self.w_embedding = w[:, D:].contiguous()
+        self.weight = tensors[self.weight_name]
         self.step = tensors[self.step_name][self.index].float().contiguous()
 
     def forward(self, residual, ctx) -> None:
         kept = ctx.memo.get(EMBEDDING_OUTPUT)
         if kept is None:
             raise ops.KernelError("stream re-injection: the embedding part did not keep its output (keep_output=True)")
-        x = torch.empty(residual.shape, dtype=ctx.dtype, device=residual.device)
-        ops.cast_add(residual, x)
-        residual.zero_()
-        L.linear(x, self.w_stream, self.step, L.RESIDUAL, residual=residual)
-        L.linear(kept, self.w_embedding, None, L.RESIDUAL, residual=residual)
+        T, D = residual.shape
+        both = torch.empty((T, 2 * D), dtype=ctx.dtype, device=residual.device)
+        ops.cast_concat(residual, kept, both)
+        L.linear(both, self.weight, self.step, L.STORE_F32, out=residual)
 
 
 register_part("stream", "reinjection", StreamReinjection)

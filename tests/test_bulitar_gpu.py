@@ -544,11 +544,12 @@ def test_greedy_generation_through_the_entry_point(tmp_path, name, dtype):
     eng.core.runner.check_device_errors()
 
 
-@pytest.mark.parametrize("T,E,top,D,F", [(300, 8, 2, 64, 48), (1000, 5, 1, 128, 2056), (257, 16, 3, 96, 136)])
+@pytest.mark.parametrize("T,E,top,D,F", [(300, 8, 2, 64, 48), (1000, 5, 1, 128, 2056), (257, 16, 3, 96, 136), (1, 8, 2, 64, 48),
+                                         (3, 8, 2, 896, 2432), (5, 16, 3, 96, 136), (60, 8, 2, 64, 48)])
 def test_grouped_experts_equal_every_expert_on_every_row(T, E, top, D, F):
-    """The routed feed-forward on the grouped contractions (pairs sorted by expert, experts padded to whole tiles)
-    against the plain sum over the chosen experts and against the same part with every expert on every row; an expert
-    that no row chose and experts with more rows than a tile are among them."""
+    """The routed feed-forward on the grouped contractions (pairs sorted by expert, experts padded to whole tiles) and,
+    for fewer pairs than experts, pair by pair, against the plain sum over the chosen experts and against the same part
+    with every expert on every row; an expert that no row chose and experts with more rows than a tile are among them."""
     from lightllm_b200.parts.moe import RoutedExperts
     if not ops.has_tcgen05():
         pytest.skip("needs the tcgen05 contraction")
@@ -561,7 +562,7 @@ def test_grouped_experts_equal_every_expert_on_every_row(T, E, top, D, F):
     W["m.correction"][E - 1] = -50.0                      # the last expert is never chosen
     part.bind({k: dev(v) for k, v in W.items()}, torch.bfloat16, DEV)
     x = torch.randn(T, D).to(torch.bfloat16)
-    assert part.grouped_pays(T)
+    assert part.grouped_pays(T) or T * top < E
     grouped, dense = torch.zeros(T, D, device=DEV), torch.zeros(T, D, device=DEV)
     part.forward(dev(x), grouped)
     ops.check_async_errors(DEV)
@@ -576,6 +577,6 @@ def test_grouped_experts_equal_every_expert_on_every_row(T, E, top, D, F):
     s = torch.sigmoid(x.double() @ Wd["m.router"].T) + Wd["m.correction"]
     order = s.sort(-1, descending=True).values
     sure = (order[:, top - 1] - order[:, top]) > 1e-3
-    assert sure.float().mean() > 0.9
+    assert sure.float().mean() > 0.9 or T < 10
     close(grouped[sure.to(DEV)], want[sure], "bfloat16", "grouped experts against the plain sum", rel=2e-2)
     close(grouped, dense.double().cpu(), "bfloat16", "grouped experts against every expert on every row", rel=2e-2)
