@@ -516,8 +516,49 @@ __global__ void __launch_bounds__(256) low_rank_up_kernel(LowRankParams p, int T
     }
 }
 
+__device__ __forceinline__ float low_rank_finish(const LowRankParams& p, int n, float z) {
+    if (p.bias) z += p.bias[n];
+    if (p.mode == 1) return 1.0f / (1.0f + expf(-z));
+    if (p.mode == 2) return -p.rate[n / p.per_rate] * (z > 20.0f ? z : log1pf(expf(z)));
+    return z;
+}
+
+// Few rows (a decode step): a warp an output, the lanes along the R inputs, so that a weight row is one coalesced read
+// and a step's few thousand outputs are spread over a hundred blocks instead of four.
+template <typename TX, typename TW, typename TO>
+__global__ void __launch_bounds__(256) low_rank_up_few_rows_kernel(LowRankParams p, int T) {
+    extern __shared__ __align__(16) float xs[];      // [T][R]
+    for (int i = threadIdx.x; i < T * p.R; i += blockDim.x) {
+        const int tl = i / p.R, r = i - tl * p.R;
+        xs[i] = llb_to_float(((const TX*)p.x)[(size_t)tl * p.x_stride + p.x_off + r]);
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31;
+    const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (n >= p.N) return;
+    const TW* wr = (const TW*)p.w + (size_t)n * p.R;
+    float wv[16];                                    // R <= 512: at most 16 inputs a lane
+#pragma unroll
+    for (int i = 0; i < 16; ++i) wv[i] = lane + 32 * i < p.R ? llb_to_float(wr[lane + 32 * i]) : 0.0f;
+    for (int tl = 0; tl < T; ++tl) {
+        float acc = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+            if (lane + 32 * i < p.R) acc = fmaf(xs[tl * p.R + lane + 32 * i], wv[i], acc);
+        acc = llb_warp_sum(acc);
+        if (lane == 0) ((TO*)p.out)[(size_t)tl * p.N + n] = llb_from_float<TO>(low_rank_finish(p, n, acc));
+    }
+}
+
 template <typename TX, typename TW>
 int launch_low_rank(const LowRankParams& p, int T, int out_dtype, cudaStream_t stream) {
+    if (T <= LR_ROWS) {
+        const dim3 grid_f((p.N + 7) / 8);
+        const size_t smem_f = (size_t)T * p.R * sizeof(float);
+        if (out_dtype == LLB_F32) low_rank_up_few_rows_kernel<TX, TW, float><<<grid_f, 256, smem_f, stream>>>(p, T);
+        else low_rank_up_few_rows_kernel<TX, TW, __nv_bfloat16><<<grid_f, 256, smem_f, stream>>>(p, T);
+        return llb_check_launch("low_rank_up_few_rows");
+    }
     const dim3 grid((p.N + 255) / 256, (T + LR_ROWS - 1) / LR_ROWS);
     const size_t smem = (size_t)LR_ROWS * ((p.R + 3) & ~3) * sizeof(float);
     if (out_dtype == LLB_F32) low_rank_up_kernel<TX, TW, float><<<grid, 256, smem, stream>>>(p, T);

@@ -179,9 +179,11 @@ def test_delta_rule_kernel_over_spans_and_slots(H, G, d, e, blocked):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_second_half_of_a_low_rank_pair(dtype):
-    torch.manual_seed(5)
-    T, off, R, H, per = 9, 7, 5, 3, 11
+@pytest.mark.parametrize("T,R", [(9, 5), (37, 5), (3, 40), (50, 64), (16, 33), (17, 96)])
+def test_second_half_of_a_low_rank_pair(dtype, T, R):
+    """Few rows take a kernel with a warp an output, more rows one with sixteen rows a block."""
+    torch.manual_seed(5 + T)
+    off, H, per = 7, 3, 11
     x = torch.randn(T, off + R + 2).to(DT[dtype])
     w = torch.randn(H * per, R).to(DT[dtype])
     bias, rate = torch.randn(H * per), torch.rand(H) + 0.5
