@@ -256,6 +256,29 @@ def main(argv=None) -> int:
             (T * D + E * 2 * F * D + T * E * F) * 2, 2 * T * E * 2 * F * D)
         run("moe_down_all_experts", lambda: L.linear(act_moe, w_dn_all, None, L.RESIDUAL, residual=resid_m),
             (T * E * F + D * E * F) * 2 + T * D * 8, 2 * T * D * E * F)
+        # the same experts on grouped contractions: the T * top pairs sorted by expert, every expert padded to whole tiles
+        ops.moe_route(x_moe, w_router, None, top, 2.5, r_ids, r_w, r_dense)
+        tiles = ops.moe_sorted_tiles(T * top, E)
+        slot = torch.empty(T * top, dtype=torch.int32, device=dev)
+        tile_group = torch.empty(tiles, dtype=torch.int32, device=dev)
+        run("moe_sort", lambda: ops.moe_sort(r_ids, E, slot, tile_group), T * top * 8)
+        ops.moe_sort(r_ids, E, slot, tile_group)
+        rows_g = tiles * ops.MOE_TILE_ROWS
+        xs_g = torch.zeros((rows_g, D), dtype=torch.bfloat16, device=dev)
+        run("moe_gather", lambda: ops.moe_gather(x_moe, slot, top, xs_g), 2 * T * top * D * 2)
+        act_g = torch.empty((rows_g, F), dtype=torch.bfloat16, device=dev)
+        y_g = torch.empty((rows_g, D), dtype=torch.float32, device=dev)
+        w_dn_rows = rn(E * D, F, dtype=torch.bfloat16, s=F ** -0.5)
+        run("moe_grouped_gate_up", lambda: ops.gemm_tcgen05_grouped(xs_g, w_gu_all, act_g, ops.EPI_SWIGLU, E, tile_group),
+            (rows_g * D + E * 2 * F * D + rows_g * F) * 2, 2 * T * top * 2 * F * D)
+        run("moe_grouped_down", lambda: ops.gemm_tcgen05_grouped(act_g, w_dn_rows, y_g, ops.EPI_STORE_F32, E, tile_group),
+            (rows_g * F + E * D * F) * 2 + rows_g * D * 4, 2 * T * top * D * F)
+        run("moe_combine", lambda: ops.moe_combine(y_g, slot, r_w, resid_m), T * top * D * 4 + 2 * T * D * 4)
+        # and pair by pair, for the pairs of one row
+        ids1 = r_ids[:1].contiguous()
+        act1 = torch.empty((top, F), dtype=torch.bfloat16, device=dev)
+        y1 = torch.empty((top, D), dtype=torch.float32, device=dev)
+        run("moe_pairs_one_row", lambda: ops.moe_pairs(x_moe[:1], ids1, w_gu_all, w_dn_rows, act1, y1), top * 3 * F * D * 2)
     if ops.attention_tcgen05_supports(hd, page) and T > 128:
         from lightllm_b200.engine.batch import cut_attention_rows, first_visible
         from lightllm_b200.parts import linear as L
