@@ -74,7 +74,7 @@ class BulitarConfig(ModelConfig):
             raise ConfigError(f"{where}: 'mixer' must be an object")
         r = ConfigReader(raw, where)
         out: Dict[str, Any] = {"heads": r.integer("heads"), "kv_heads": r.integer("kv_heads"), "dim": r.integer("dim"),
-                               "vdim": r.integer("vdim"), "conv": r.integer("conv")}
+                               "vdim": r.integer("vdim"), "conv": r.integer("conv", None)}          # no 'conv': no convolution
         if out["heads"] % out["kv_heads"]:
             raise ConfigError(f"{where}: 'heads' {out['heads']} is not a multiple of 'kv_heads' {out['kv_heads']}")
         if kind == "attention":
@@ -137,9 +137,9 @@ class BulitarConfig(ModelConfig):
         if lp is not None:
             lr_ = ConfigReader(lp, f"{where}: loop")
             start, stop, times = lr_.integer("start", minimum=0), lr_.integer("stop"), lr_.integer("times")
-            if not 0 <= start < stop <= len(layers):
+            if not 0 <= start <= stop <= len(layers):
                 raise ConfigError(f"{where}: loop: layers {start} .. {stop} - 1 are not a stretch of the {len(layers)} layers")
-            loop = (start, stop, times)
+            loop = (start, stop, times) if stop > start else None          # an empty stretch: nothing is run again
         # the ranks read from tensor shapes are written back, so that the configuration stands on its own
         raw_out = dict(raw)
         if tensor_shapes is not None:
@@ -168,14 +168,14 @@ def bulitar_spec(cfg: BulitarConfig) -> ModelSpec:
                                                "style": "interleaved", "scaling": rot["scaling"]})
             mixer = PartSpec("conv_attention", {
                 "hidden_size": D, "num_heads": m["heads"], "num_kv_heads": m["kv_heads"], "head_dim": m["dim"],
-                "v_head_dim": m["vdim"], "position": position, "conv_taps": m["conv"], "qkv_bias": True, "out_bias": True,
+                "v_head_dim": m["vdim"], "position": position, "conv_taps": m["conv"] or 0, "qkv_bias": True, "out_bias": True,
                 "chunk": m["chunk"], "scale": m["scale"], "qk_unit_rms": True, "qk_norm_eps": eps,
                 "names": {"q": "q", "k": "k", "v": "v", "o": "o"}, "bias_ending": "b", "conv_ending": "conv", **plain},
                 f"{p}.mix")
         else:
             mixer = PartSpec("channel_delta", {
                 "hidden_size": D, "num_heads": m["heads"], "num_qk_heads": m["kv_heads"], "head_dim": m["dim"],
-                "v_head_dim": m["vdim"], "conv_taps": m["conv"], "decay_rank": m["decay_rank"], "gate_rank": m["gate_rank"],
+                "v_head_dim": m["vdim"], "conv_taps": m["conv"] or 0, "decay_rank": m["decay_rank"], "gate_rank": m["gate_rank"],
                 "norm_eps": eps, "conv_ending": "conv",
                 "names": {"q": "q", "k": "k", "v": "v", "b": "b", "a1": "a1", "a2": "a2", "g1": "g1", "g2": "g2", "o": "o",
                           "A_log": "A_log", "dt_bias": "dt_bias", "norm": "norm"}, **plain}, f"{p}.mix")
@@ -206,7 +206,9 @@ def bulitar_spec(cfg: BulitarConfig) -> ModelSpec:
         embedding=PartSpec("token_embedding", {"vocab_size": cfg.vocab, "hidden_size": D, "weight_name": "embed",
                                                "scale": cfg.embedding_scale, "keep_output": cfg.loop is not None}, ""),
         layers=layers, run=run, final_norm=layer_norm("final.norm"),
-        head=PartSpec("lm_head", {"vocab_size": cfg.vocab, "hidden_size": D, "weight_name": "head"}, ""))
+        head=PartSpec("lm_head", {"vocab_size": cfg.vocab, "hidden_size": D, "weight_name": "head"}, ""),
+        # a model without a loop (or with an empty one) may still carry the loop's tensors
+        ignored_suffixes=("loop.in", "loop.step") if cfg.loop is None else ())
 
 
 register_architecture("Bulitar", BulitarConfig.from_dict, bulitar_spec, reads_shapes=True)

@@ -22,7 +22,8 @@ class ConvAttentionMixer(AttentionMixer):
     """Grouped-query attention over the paged cache in which
 
     * every channel of q, k and v (bias included) first passes a causal convolution of ``conv_taps`` taps over time
-      (``<projection>.conv``, ``[channels, taps]``, the last tap on the current token, zeros before the sequence);
+      (``<projection>.conv``, ``[channels, taps]``, the last tap on the current token, zeros before the sequence;
+      ``conv_taps = 0``: no convolution and no such tensors);
     * q and k are then rotated by position (``position``: adjacent or half-split pairs, optionally YaRN-scaled, with
       its magnitude applied) and, with ``qk_unit_rms``, divided head by head by their root mean square;
     * values may be of another width than keys (``v_head_dim``); ``scale``, ``window`` and ``chunk`` as the plain mixer;
@@ -43,8 +44,8 @@ class ConvAttentionMixer(AttentionMixer):
                  scale: Optional[float] = None, qk_unit_rms: bool = False, qk_norm_eps: float = 1e-6,
                  names: Optional[Dict[str, str]] = None, weight_suffix: str = ".weight", bias_ending: str = "bias",
                  conv_ending: str = "conv"):
-        if conv_taps < 1:
-            raise ValueError(f"a convolution needs at least one tap, got {conv_taps}")
+        if conv_taps < 0:
+            raise ValueError(f"a convolution has a number of taps (or 0 for none), got {conv_taps}")
         super().__init__(prefix, hidden_size, num_heads, num_kv_heads, head_dim, position=position, qkv_bias=qkv_bias,
                          out_bias=out_bias, window=window, scale=scale, names=names, weight_suffix=weight_suffix,
                          v_head_dim=v_head_dim, chunk=chunk)
@@ -72,7 +73,8 @@ class ConvAttentionMixer(AttentionMixer):
             specs += [WeightSpec(self._n(p, self.bias_ending), (n,)) for p, n in rows.items()]
         if self.out_bias:
             specs.append(WeightSpec(self._n("o", self.bias_ending), (D,)))
-        specs += [WeightSpec(self._n(p, self.conv_ending), (n, self.conv_taps), init=("normal", 0.5)) for p, n in rows.items()]
+        if self.conv_taps > 0:
+            specs += [WeightSpec(self._n(p, self.conv_ending), (n, self.conv_taps), init=("normal", 0.5)) for p, n in rows.items()]
         return specs + self.position.weight_specs()
 
     def bind(self, tensors, dtype, device) -> None:
@@ -84,7 +86,10 @@ class ConvAttentionMixer(AttentionMixer):
             self.b_qkv = torch.cat([tensors[self._n(p, self.bias_ending)].float() for p in "qkv"]).contiguous()
         if self.out_bias:
             self.b_o = tensors[self._n("o", self.bias_ending)].float().contiguous()
-        self.w_conv = torch.cat([tensors[self._n(p, self.conv_ending)].float() for p in "qkv"], dim=0).contiguous()
+        if self.conv_taps > 0:
+            self.w_conv = torch.cat([tensors[self._n(p, self.conv_ending)].float() for p in "qkv"], dim=0).contiguous()
+        else:          # no convolution: one tap of weight one
+            self.w_conv = torch.ones((self.channels, 1), dtype=torch.float32, device=device)
         self.position.bind(tensors, dtype, device)
 
     def prepare(self, ctx, cache=None) -> None:
@@ -111,7 +116,7 @@ class ConvAttentionMixer(AttentionMixer):
                          ctx.slot_mapping[cache.group], freq, getattr(self.position, "magnitude", 1.0),
                          fuse_tail=ctx.decode_only)
         if self.conv_taps > 1 and not ctx.decode_only:
-            ops.conv_tail_update(fused, 0, self.channels, self.conv_taps, spans, cache.state, 0)
+            ops.conv_tail_update(fused, 0, self.channels, self.conv_taps, spans, cache.state, 0)          # (its taps: w_conv's)
         attn = torch.empty((T, H * vd), dtype=x.dtype, device=x.device)
         self.attend(q, cache, ctx, attn)
         L.linear(attn, self.w_o, self.b_o, L.RESIDUAL, residual=residual)

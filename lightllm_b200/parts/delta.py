@@ -40,8 +40,8 @@ class ChannelDeltaMixer(Mixer):
                  names: Optional[Dict[str, str]] = None, weight_suffix: str = ".weight", conv_ending: str = "conv"):
         if num_heads % num_qk_heads:
             raise ValueError(f"{num_heads} heads are not a multiple of {num_qk_heads} q/k heads")
-        if conv_taps < 1:
-            raise ValueError(f"a convolution needs at least one tap, got {conv_taps}")
+        if conv_taps < 0:
+            raise ValueError(f"a convolution has a number of taps (or 0 for none), got {conv_taps}")
         self.prefix, self.hidden_size = prefix, hidden_size
         self.num_heads, self.num_qk_heads, self.head_dim, self.v_head_dim = num_heads, num_qk_heads, head_dim, v_head_dim
         self.conv_taps, self.decay_rank, self.gate_rank, self.norm_eps = int(conv_taps), decay_rank, gate_rank, float(norm_eps)
@@ -57,14 +57,15 @@ class ChannelDeltaMixer(Mixer):
         return f"{self.prefix}.{self.names[which]}" + (self.weight_suffix if weight else "")
 
     def cache_spec(self) -> CacheSpec:
-        return CacheSpec(state=StateSpec((self.state_floats + (self.conv_taps - 1) * self.channels,), "float32"))
+        return CacheSpec(state=StateSpec((self.state_floats + max(0, self.conv_taps - 1) * self.channels,), "float32"))
 
     def weight_specs(self) -> List[WeightSpec]:
         D, H, G, hd, vd = self.hidden_size, self.num_heads, self.num_qk_heads, self.head_dim, self.v_head_dim
         rows = {"q": G * hd, "k": G * hd, "v": H * vd}
         specs = [WeightSpec(self._n(p), (n, D)) for p, n in rows.items()]
-        specs += [WeightSpec(f"{self._n(p, False)}.{self.conv_ending}", (n, self.conv_taps), init=("normal", 0.5))
-                  for p, n in rows.items()]
+        if self.conv_taps > 0:
+            specs += [WeightSpec(f"{self._n(p, False)}.{self.conv_ending}", (n, self.conv_taps), init=("normal", 0.5))
+                      for p, n in rows.items()]
         specs += [WeightSpec(self._n("b"), (H, D)), WeightSpec(self._n("a1"), (self.decay_rank, D)),
                   WeightSpec(self._n("a2"), (H * hd, self.decay_rank), init=("normal", 0.2)),
                   WeightSpec(self._n("g1"), (self.gate_rank, D)),
@@ -79,7 +80,10 @@ class ChannelDeltaMixer(Mixer):
         ws = [tensors[self._n(p)] for p in ("q", "k", "v", "b", "a1", "g1")]
         wdt = torch.float32 if any(w.dtype == torch.float32 for w in ws) else ws[0].dtype
         self.w_fused = torch.cat([w.to(wdt) for w in ws], dim=0).contiguous()
-        self.w_conv = torch.cat([tensors[f"{self._n(p, False)}.{self.conv_ending}"].float() for p in "qkv"], dim=0).contiguous()
+        if self.conv_taps > 0:
+            self.w_conv = torch.cat([tensors[f"{self._n(p, False)}.{self.conv_ending}"].float() for p in "qkv"], dim=0).contiguous()
+        else:          # no convolution: one tap of weight one
+            self.w_conv = torch.ones((self.channels, 1), dtype=torch.float32, device=device)
         self.w_a2, self.w_g2 = tensors[self._n("a2")].contiguous(), tensors[self._n("g2")].contiguous()
         self.w_o = tensors[self._n("o")]
         self.rate = torch.exp(tensors[self._n("A_log", False)].float()).contiguous()
@@ -103,7 +107,7 @@ class ChannelDeltaMixer(Mixer):
         tail_off = self.state_floats
         ops.conv_prepare(fused, 0, self.channels, self.w_conv, segments, spans, cache.state, tail_off,
                          fuse_tail=ctx.decode_only)
-        if not ctx.decode_only:
+        if not ctx.decode_only and self.conv_taps > 1:
             ops.conv_tail_update(fused, 0, self.channels, self.conv_taps, spans, cache.state, tail_off)
         c = self.channels
         decay = torch.empty((T, H * hd), **f32)

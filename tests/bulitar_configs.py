@@ -10,7 +10,9 @@ import torch
 
 
 def _attn(heads, kv_heads, dim, vdim, conv, chunk, rot_dims, base=10000.0, scaling=None, scale=None):
-    m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": conv, "scale": scale or dim ** -0.5}
+    m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale or dim ** -0.5}
+    if conv is not None:          # (no 'conv': the layer has no convolution and no such tensors)
+        m["conv"] = conv
     if chunk is not None:
         m["mask"] = {"size": chunk}
     if rot_dims is not None:
@@ -55,10 +57,10 @@ BUL_V = {"architecture": "Bulitar", "vocab": 517, "width": 128, "embedding": {"s
     _moe(_delta(4, 1, 64, 32, 3, 24, 24), 64, 6, 2, 2.5),
     _moe(_delta(1, 1, 256, 16, 2, 8, 8), 64, 4, 1, 1.0),
 ]}
-# W: what the others make unequal is equal or 1 here: no loop, one tap (no convolution state at all), no mask, no
-# rotation in one layer and a full one in the other, one expert, one head.
+# W: what the others make unequal is equal, 1 or absent here: no loop, no convolution in one layer and one tap in the
+# others (no convolution state at all), no mask, no rotation in one layer and a full one in the other, one expert, one head.
 BUL_W = {"architecture": "Bulitar", "vocab": 97, "width": 32, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5}, "layers": [
-    _moe(_attn(1, 1, 16, 16, 1, None, None), 24, 1, 1, 1.0),
+    _moe(_attn(1, 1, 16, 16, None, None, None), 24, 1, 1, 1.0),
     _moe(_delta(1, 1, 16, 16, 1, 4, 4), 24, 2, 2, 1.0),
     _moe(_attn(2, 1, 8, 8, 1, 5, 8), 24, 3, 2, 1.0),
 ]}
@@ -88,11 +90,13 @@ def tensor_shapes(cfg) -> Dict[str, tuple]:
     for i, layer in enumerate(cfg["layers"]):
         p, m = f"l{i}.", layer["mixer"]
         out[p + "norm1"] = (D,)
-        H, G, dim, vdim, taps = m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["conv"]
+        H, G, dim, vdim, taps = m["heads"], m["kv_heads"], m["dim"], m["vdim"], m.get("conv")
         if layer["type"] == "attention":
             rows = {"q": H * dim, "k": G * dim, "v": G * vdim}
             for n, r in rows.items():
-                out[p + f"mix.{n}"], out[p + f"mix.{n}.b"], out[p + f"mix.{n}.conv"] = (r, D), (r,), (r, taps)
+                out[p + f"mix.{n}"], out[p + f"mix.{n}.b"] = (r, D), (r,)
+                if taps:
+                    out[p + f"mix.{n}.conv"] = (r, taps)
             out[p + "mix.o"], out[p + "mix.o.b"] = (D, H * vdim), (D,)
         else:
             rows = {"q": G * dim, "k": G * dim, "v": H * vdim}

@@ -24,10 +24,6 @@ def unit_rms(x: torch.Tensor, eps: float) -> torch.Tensor:
     return x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)
 
 
-def gelu_tanh(z):
-    return 0.5 * z * (1 + torch.tanh(math.sqrt(2 / math.pi) * (z + 0.044715 * z ** 3)))
-
-
 def short_conv(u: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     """``y[t, c] = sum_j w[c, j] * u[t - taps + 1 + j, c]`` with zeros before the first token."""
     T, C = u.shape
@@ -98,7 +94,7 @@ def attention_mixer(h: torch.Tensor, W: Dict[str, torch.Tensor], p: str, m: dict
 
     def proj(name):
         y = h @ W[f"{p}.{name}"].T + W[f"{p}.{name}.b"]
-        return short_conv(y, W[f"{p}.{name}.conv"])
+        return short_conv(y, W[f"{p}.{name}.conv"]) if f"{p}.{name}.conv" in W else y
     q = proj("q").view(T, H, dim)
     k = proj("k").view(T, G, dim)
     v = proj("v").view(T, G, vdim)

@@ -53,7 +53,7 @@ def test_run_list_follows_the_loop():
     (lambda c: c["layers"][0]["mixer"].update(heads=3), "multiple"),
     (lambda c: c["layers"][0]["mixer"]["rot"].update(dims=7), "dims"),
     (lambda c: c["layers"][0]["mixer"]["rot"]["scaling"].pop("slow"), "slow"),
-    (lambda c: c["layers"][0]["mixer"].pop("conv"), "conv"),
+    (lambda c: c["layers"][0]["mixer"].update(conv=0), "conv"),
     (lambda c: c["layers"][0]["mlp"].update(kind="dense"), "moe"),
     (lambda c: c["layers"][0]["mlp"]["router"].update(top=9), "top"),
     (lambda c: c["loop"].update(stop=9), "loop"),
@@ -64,6 +64,18 @@ def test_configuration_errors_name_the_key(edit, match):
     edit(cfg)
     with pytest.raises(ConfigError, match=match):
         config_from_dict(cfg)
+
+
+def test_an_empty_loop_and_a_layer_without_convolution():
+    cfg = config("U")
+    cfg["loop"] = {"start": 2, "stop": 2, "times": 3}
+    cfg["layers"][0]["mixer"].pop("conv")
+    spec = model_spec_for(config_from_dict(cfg))
+    assert [e.layer for e in spec.run] == [0, 1, 2, 3] and all(e.enter is None for e in spec.run)
+    assert [i for i, _ in P.run_list(dict(cfg, loop=None))] == [0, 1, 2, 3]
+    names = {s.name for s in Model(spec).weight_specs()}
+    assert "l0.mix.q.conv" not in names and "l2.mix.q.conv" in names and "loop.in" not in names
+    assert spec.ignored_suffixes == ("loop.in", "loop.step")          # such a checkpoint may still carry them
 
 
 def test_pages_of_earlier_chunks_are_given_back():
