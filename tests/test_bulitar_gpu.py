@@ -582,3 +582,27 @@ def test_grouped_experts_equal_every_expert_on_every_row(T, E, top, D, F):
     assert sure.float().mean() > 0.9 or T < 10
     close(grouped[sure.to(DEV)], want[sure], "bfloat16", "grouped experts against the plain sum", rel=2e-2)
     close(grouped, dense.double().cpu(), "bfloat16", "grouped experts against every expert on every row", rel=2e-2)
+
+
+@pytest.mark.parametrize("name", ["V", "X"])
+def test_chosen_experts_through_the_engine_in_bfloat16(tmp_path, name):
+    """The bfloat16 engine with fewer experts chosen than there are: single tokens take the experts pair by pair, portions
+    of 48 rows or more the grouped contractions (V; X's widths keep every expert on every row), the rest every expert on
+    every row.  So that rounding cannot flip a choice, the corrections lie 2 apart (the same experts win for every token;
+    their weights still follow the token's scores)."""
+    cfg = config(name)
+    w = random_weights(cfg, 12, store=torch.bfloat16)
+    for k in w:
+        if k.endswith("correction"):
+            w[k] = (-2.0 * torch.arange(w[k].numel(), dtype=torch.float32)).to(torch.bfloat16)
+    d = write_model(cfg, w, str(tmp_path / f"bul_{name}_experts"))
+    wd = {k: v.double() for k, v in w.items()}
+    rng = random.Random(9)
+    toks = [rng.randrange(cfg["vocab"]) for _ in range(150)]
+    plain = plain_logits(toks, wd, cfg)
+    core = core_for(d, "bfloat16", name)
+    got = stepwise(core, "a", toks, [100, 20, 2, 7])          # grouped, every expert on every row, then pair by pair
+    err = error(got, plain, "bfloat16")
+    record(f"Bulitar {name} bfloat16 chosen experts", err, logits_std(plain))
+    assert err <= atol_for(name, "bfloat16", plain)
+    core.runner.check_device_errors()
