@@ -606,3 +606,48 @@ def test_chosen_experts_through_the_engine_in_bfloat16(tmp_path, name):
     record(f"Bulitar {name} bfloat16 chosen experts", err, logits_std(plain))
     assert err <= atol_for(name, "bfloat16", plain)
     core.runner.check_device_errors()
+
+
+def test_command_lines_serve_the_design(tmp_path):
+    """``random_model`` writes a folder from a config.json of the design (the ranks of the low-rank pairs given in it);
+    ``generate`` continues a prompt greedily as the plain implementation does and samples the same tokens for the same
+    seed; ``bench_server`` runs its users."""
+    import json
+    import os
+    import re
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+    def run_cli(module, *args):
+        env = dict(os.environ, PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""))
+        proc = subprocess.run([sys.executable, "-m", module, *map(str, args)], stdout=subprocess.PIPE, stderr=subprocess.PIPE,
+                              text=True, env=env, timeout=600, cwd=root)
+        assert proc.returncode == 0, proc.stderr[-3000:]
+        return proc.stdout
+
+    cfg = config("U")
+    cfg_path = str(tmp_path / "config.json")
+    with open(cfg_path, "w") as f:
+        json.dump(cfg, f)
+    d = str(tmp_path / "model")
+    run_cli("lightllm_b200.cli.random_model", cfg_path, d, 4, "--store-dtype", "float32")
+    from tests.plain.qwen2_plain import read_safetensors
+    w = {k: v.double() for k, v in read_safetensors(os.path.join(d, "model.safetensors")).items()}
+    prompt = [5, 17, 3, 99, 250, 7]
+    out = run_cli("lightllm_b200.cli.generate", d, *prompt, "--temperature", 0, "--max-new-tokens", 8, "--dtype", "float32",
+                  "--max-seq-len", 64)
+    got = [int(t) for t in re.search(r"generated:\s*([\d ]+)", out).group(1).split()]
+    seq = list(prompt)
+    for tok in got:
+        lg = P.forward(seq, cfg, w)[0][-1]
+        top = torch.topk(lg, 2).values
+        assert tok == int(torch.argmax(lg)) or float(top[0] - top[1]) < 1e-4, (seq, tok)
+        seq.append(tok)
+    assert len(got) == 8
+    pick = lambda s: re.search(r"generated:\s*([\d ]+)", s).group(1)
+    a = run_cli("lightllm_b200.cli.generate", d, 1, 2, 3, "--seed", 5, "--max-seq-len", 64)
+    b = run_cli("lightllm_b200.cli.generate", d, 1, 2, 3, "--seed", 5, "--max-seq-len", 64)
+    assert pick(a) == pick(b)
+    out = run_cli("lightllm_b200.cli.bench_server", d, 128, 64)
+    assert "Hidden dim=44" in out and "vocab=301" in out
